@@ -160,6 +160,7 @@ class CacheManager:
         self.max_num_seqs = int(max_num_seqs)
         self.max_seq_len = int(max_seq_len)
         self.max_pages_per_seq = -(-self.max_seq_len // self.page_size)
+        self.num_rows = self.max_num_seqs + int(extra_table_rows)     # rows of every per-slot table and state
         counts = [num_pages] * len(self.groups) if isinstance(num_pages, int) else list(num_pages)
         if len(counts) != len(self.groups):
             raise ValueError("num_pages must be one number or one per group")

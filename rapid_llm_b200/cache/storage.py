@@ -38,7 +38,7 @@ class CacheStorage:
             need = group.need
             shape = (len(group.entries), pool.num_pages + 1, *need.page_shape(manager.page_size))
             self.pages.append(torch.zeros(shape, dtype=dtype, device=device))
-        self.num_rows = manager.block_tables[0].shape[0] if manager.block_tables else manager.max_num_seqs
+        self.num_rows = manager.num_rows       # a model without cache pages still has its state rows, the padding slot's too
         self.block_tables = [
             torch.zeros(table.shape, dtype=torch.int32, device=device) for table in manager.block_tables
         ]

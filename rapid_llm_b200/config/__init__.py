@@ -2,6 +2,7 @@
 
 from .engine_config import EngineConfig, parse_dtype
 from .model_spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+from .kopatar import KopatarConfig
 from .qwen3 import Qwen3Config
 from .registry import (
     load_config,
@@ -12,9 +13,11 @@ from .registry import (
 )
 
 register_architecture(Qwen3Config)
+register_architecture(KopatarConfig)
 
 __all__ = [
     "EngineConfig",
+    "KopatarConfig",
     "LayerSpec",
     "ModelSpec",
     "PartSpec",

@@ -52,9 +52,10 @@ class LayerSpec:
 
     arrangement: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: PartSpec | None     # None: the layer is its mixer's half alone
     norm: PartSpec
     prefix: str
+    names: Mapping[str, str] | None = None   # checkpoint sub-prefixes of the layer's parts, where they differ from the arrangement's
 
 
 @dataclass(frozen=True)
@@ -63,12 +64,19 @@ class ScheduleEntry:
 
     ``layer`` indexes :attr:`ModelSpec.layers`; the same layer may be named by
     several entries (its weights are then shared, each entry still owns a cache
-    of its own).  ``cache_from`` names an *earlier entry* whose cache this entry
-    reads instead of writing one.
+    and a state of its own).  ``cache_from`` names an *earlier entry* whose cache
+    this entry reads instead of writing one.
+
+    An entry that opens a pass over a run of layers says so with ``pass_index``:
+    row ``pass_index`` of the model's pass offsets (:attr:`ModelSpec.pass_offset`)
+    joins the residual stream right before the entry's layer, after the
+    embedding's output if ``add_embedding`` is set.
     """
 
     layer: int
     cache_from: int | None = None
+    pass_index: int | None = None
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)
@@ -87,6 +95,8 @@ class ModelSpec:
     final_norm_prefix: str = "model.norm."
     embedding_prefix: str = "model.embed_tokens."
     head_prefix: str = "lm_head."
+    pass_offset: PartSpec | None = None      # a learned row per pass of a looped run of layers
+    pass_offset_prefix: str = ""
 
     def validate(self) -> None:
         if not self.layers:
@@ -99,6 +109,10 @@ class ModelSpec:
                     f"schedule entry {index} names layer {entry.layer}, "
                     f"but the model has {len(self.layers)} layers"
                 )
+            if entry.pass_index is not None and self.pass_offset is None:
+                raise ValueError(f"schedule entry {index} opens pass {entry.pass_index}, but the model has no pass offsets")
+            if entry.add_embedding and entry.pass_index is None:
+                raise ValueError(f"schedule entry {index} adds the embedding without opening a pass")
             if entry.cache_from is not None:
                 if not 0 <= entry.cache_from < index:
                     raise ValueError(

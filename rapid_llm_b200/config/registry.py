@@ -3,8 +3,8 @@
 The reference keys its registry on ``config.json``'s ``model_type`` and imports
 the model class lazily (``rapid_llm/models/registry.py:20-78``); its cheap sniff
 of the file has three distinct errors (``rapid_llm/models/config.py:42-62``).
-Here the key is the first entry of ``architectures`` with ``model_type`` as the
-fallback, and the value is the architecture's configuration class, whose
+Here the key is the first entry of ``architectures`` (or the string ``architecture``) with
+``model_type`` as the fallback, and the value is the architecture's configuration class, whose
 ``to_spec()`` yields the layer list the generic model runs.
 """
 
@@ -48,7 +48,7 @@ def supported_architectures() -> list[str]:
 
 def resolve_architecture(raw: Mapping[str, Any]) -> type:
     """The configuration class for a parsed ``config.json``."""
-    names = raw.get("architectures") or []
+    names = raw.get("architectures") or raw.get("architecture") or []
     if isinstance(names, str):
         names = [names]
     for name in names:
@@ -81,4 +81,7 @@ def read_config_json(model_dir: str | Path) -> dict[str, Any]:
 def load_config(model_dir: str | Path, overrides: Mapping[str, Any] | None = None):
     """Read ``config.json`` of a model folder into its architecture's configuration."""
     raw = read_config_json(model_dir)
-    return resolve_architecture(raw).from_dict(raw, overrides)
+    config_class = resolve_architecture(raw)
+    if hasattr(config_class, "from_folder"):      # an architecture whose file leaves sizes to the tensors' shapes
+        return config_class.from_folder(model_dir, raw, overrides)
+    return config_class.from_dict(raw, overrides)

@@ -61,6 +61,9 @@ __global__ void embedding_kernel(T* __restrict__ out, const T* __restrict__ tabl
 //   mode 1: r = x + residual
 //   mode 2: r = x, residual untouched and may be null (a plain norm)
 // With `write_residual` the sum is stored back to `residual` (float32).
+// `extra_rows` (a row per token, the dtype of x) and `extra_vector` (float32, one row for all
+// tokens), where given, are added to r in that order before it is stored or normed: what a model
+// feeds into the stream between two layers.
 // out = r * rsqrt(mean(r^2) + eps) * weight, all in float32, rounded once.
 //
 // kVector: hidden is a multiple of 8 and the block has at least hidden / 8 threads; a thread
@@ -69,7 +72,8 @@ template <typename TX, typename TOut, bool kVector>
 __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, float* __restrict__ residual,
                                    const float* __restrict__ weight, TOut* __restrict__ out,
                                    const int* __restrict__ row_index, int hidden, float eps,
-                                   int mode, int write_residual) {
+                                   int mode, int write_residual, const TX* __restrict__ extra_rows,
+                                   const float* __restrict__ extra_vector) {
   extern __shared__ float row_values[];  // [hidden] on the element-by-element path
   __shared__ float scratch[32];
   pdl_trigger();
@@ -77,6 +81,7 @@ __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, float* __restrict__
   const int in_row = row_index ? row_index[out_row] : out_row;
   const TX* xr = x + static_cast<size_t>(in_row) * hidden;
   float* rr = residual ? residual + static_cast<size_t>(in_row) * hidden : nullptr;
+  const TX* er = extra_rows ? extra_rows + static_cast<size_t>(in_row) * hidden : nullptr;
   TOut* o = out + static_cast<size_t>(out_row) * hidden;
 
   if constexpr (kVector) {
@@ -93,6 +98,18 @@ __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, float* __restrict__
         load8(rr + at, r);
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] += r[i];
+      }
+      if (er) {
+        float extra[8];
+        load8(er + at, extra);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] += extra[i];
+      }
+      if (extra_vector) {
+        float extra[8];
+        load8(extra_vector + at, extra);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] += extra[i];
       }
       if (write_residual) store8(rr + at, v);
 #pragma unroll
@@ -111,6 +128,8 @@ __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, float* __restrict__
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
       float v = to_float(xr[i]);
       if (mode == 1) v += rr[i];
+      if (er) v += to_float(er[i]);
+      if (extra_vector) v += extra_vector[i];
       if (write_residual) rr[i] = v;
       row_values[i] = v;
       sum_sq += v * v;
@@ -210,19 +229,22 @@ int rl_embedding(int dtype, void* out, const void* table, const int* ids, const 
 // x and out are `dtype`; residual and weight are float32.
 int rl_add_rmsnorm(int dtype, const void* x, float* residual, const float* weight, void* out,
                    const int* row_index, int rows, int hidden, float eps, int mode,
-                   int write_residual, int pdl, cudaStream_t stream) {
+                   int write_residual, const void* extra_rows, const float* extra_vector, int pdl,
+                   cudaStream_t stream) {
   if (rows == 0) return 0;
   if (mode < 0 || mode > 2 || (mode == 1 && residual == nullptr) ||
       (write_residual && residual == nullptr) || hidden <= 0)
     return static_cast<int>(cudaErrorInvalidValue);
   const bool vector = hidden % 8 == 0 && hidden <= 8 * 1024 && rl::aligned16(x) && rl::aligned16(out) &&
-                      rl::aligned16(weight) && (residual == nullptr || rl::aligned16(residual));
+                      rl::aligned16(weight) && (residual == nullptr || rl::aligned16(residual)) &&
+                      rl::aligned16(extra_rows) && rl::aligned16(extra_vector);
   RL_DISPATCH_DTYPE(dtype, {
     if (vector) {
       const int threads = (hidden / 8 + 31) / 32 * 32;
       return rl::launch_kernel(rl::add_rmsnorm_kernel<scalar_t, scalar_t, true>, dim3(rows), dim3(threads), 0,
                                stream, pdl != 0, static_cast<const scalar_t*>(x), residual, weight,
-                               static_cast<scalar_t*>(out), row_index, hidden, eps, mode, write_residual);
+                               static_cast<scalar_t*>(out), row_index, hidden, eps, mode, write_residual,
+                               static_cast<const scalar_t*>(extra_rows), extra_vector);
     }
     const size_t smem = static_cast<size_t>(hidden) * sizeof(float);
     if (smem > 200 * 1024) return static_cast<int>(cudaErrorInvalidValue);
@@ -236,7 +258,8 @@ int rl_add_rmsnorm(int dtype, const void* x, float* residual, const float* weigh
     }
     return rl::launch_kernel(kernel, dim3(rows), dim3(threads), smem, stream, pdl != 0,
                              static_cast<const scalar_t*>(x), residual, weight, static_cast<scalar_t*>(out),
-                             row_index, hidden, eps, mode, write_residual);
+                             row_index, hidden, eps, mode, write_residual,
+                             static_cast<const scalar_t*>(extra_rows), extra_vector);
   });
   return 0;
 }

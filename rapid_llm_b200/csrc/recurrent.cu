@@ -1,0 +1,541 @@
+// Kernels of the mixers that carry a state of fixed size per request instead of (or beside) cached
+// keys: short causal convolutions, decays and step sizes, the recurrence itself, the norm and gate
+// that follow it, and the activation of the dense feed-forward.
+//
+// A step is a packed ragged batch: entry e owns rows cu_seqlens[e] .. cu_seqlens[e + 1] - 1, its
+// request sits in slot entry_slot[e] and had entry_start[e] tokens before this step.  State lives in
+// one float32 row per slot (`state + slot * state_stride + offset`); a request at position 0 starts
+// from zeros whatever the row holds, so a slot needs no clearing when it changes hands.  Everything a
+// recurrence consumes (decays, step sizes, gates, unit vectors, the state) is float32 in both engine
+// precisions; the recurrence runs token by token in a fixed order, so a row's result does not depend
+// on how the tokens were cut into steps or on what else is in the batch.
+#include "common.cuh"
+
+namespace rl {
+
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+
+// The entry that owns packed row t: the last e with cu_seqlens[e] <= t.
+__device__ __forceinline__ int entry_of(const int* __restrict__ cu_seqlens, int entries, int t) {
+  int lo = 0, hi = entries - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (cu_seqlens[mid] <= t) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+constexpr int kMaxTaps = 16;
+
+// ------------------------------------------------------------ short causal convolution
+// out[t, c] = silu(bias[c] + sum_d taps[c, K - 1 - d] * x[t - d, c]) over the request's own tokens:
+// those of this step from the rows of x, the K - 1 before them from the slot's tail (float32,
+// [K - 1, C], oldest first), zeros before position 0.  x is columns col0 .. col0 + C - 1 of rows of
+// length x_stride.
+template <typename T>
+__global__ void causal_conv_silu_kernel(const T* __restrict__ x, int x_stride, int col0,
+                                        const float* __restrict__ taps, const float* __restrict__ bias,
+                                        const float* __restrict__ state, long long state_stride, int state_off,
+                                        float* __restrict__ out, const int* __restrict__ cu_seqlens,
+                                        const int* __restrict__ entry_slot, const int* __restrict__ entry_start,
+                                        int entries, int tokens, int C, int K, int slots, int* __restrict__ fault) {
+  pdl_trigger();
+  pdl_wait();
+  const long long total = static_cast<long long>(tokens) * C;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(idx / C), c = static_cast<int>(idx - static_cast<long long>(t) * C);
+    const int e = entry_of(cu_seqlens, entries, t);
+    const int local = t - cu_seqlens[e], start = entry_start[e];
+    int slot = entry_slot[e];
+    if (slot < 0 || slot >= slots) {
+      atomicOr(fault, kFaultSlot);
+      slot = 0;
+    }
+    const float* tail = state + slot * state_stride + state_off;
+    float acc = bias ? bias[c] : 0.0f;
+    for (int d = 0; d < K; ++d) {
+      const int at = local - d;
+      float v = 0.0f;
+      if (at >= 0) {
+        v = to_float(x[static_cast<size_t>(t - d) * x_stride + col0 + c]);
+      } else if (start + at >= 0) {
+        v = tail[static_cast<size_t>(K - 1 + at) * C + c];
+      }
+      acc += taps[static_cast<size_t>(c) * K + (K - 1 - d)] * v;
+    }
+    out[idx] = silu_f(acc);
+  }
+}
+
+// The slot's tail after the step: the last K - 1 inputs of the request, taken from this step's rows
+// and, where the step brought fewer, from the old tail.  A thread reads all it needs before it writes.
+template <typename T>
+__global__ void conv_tail_update_kernel(const T* __restrict__ x, int x_stride, int col0,
+                                        float* __restrict__ state, long long state_stride, int state_off,
+                                        const int* __restrict__ cu_seqlens, const int* __restrict__ entry_slot,
+                                        const int* __restrict__ entry_start, int entries, int C, int K, int slots) {
+  pdl_trigger();
+  pdl_wait();
+  const long long total = static_cast<long long>(entries) * C;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int e = static_cast<int>(idx / C), c = static_cast<int>(idx - static_cast<long long>(e) * C);
+    const int slot = entry_slot[e];
+    if (slot < 0 || slot >= slots) continue;
+    const int first = cu_seqlens[e], length = cu_seqlens[e + 1] - first, start = entry_start[e];
+    float* tail = state + slot * state_stride + state_off;
+    float fresh[kMaxTaps];
+    for (int j = 0; j < K - 1; ++j) {
+      const int at = length - (K - 1) + j;      // index among this step's tokens of the request
+      float v = 0.0f;
+      if (at >= 0) {
+        v = to_float(x[static_cast<size_t>(first + at) * x_stride + col0 + c]);
+      } else if (start + at >= 0) {
+        v = tail[static_cast<size_t>(K - 1 + at) * C + c];
+      }
+      fresh[j] = v;
+    }
+    for (int j = 0; j < K - 1; ++j) tail[static_cast<size_t>(j) * C + c] = fresh[j];
+  }
+}
+
+// ------------------------------------------------------------ decays and step sizes
+// step[t, c] = softplus(x[t, c] + bias[c]); decay[t, c] = exp(-exp(a_log[c / per]) * step[t, c]).
+template <typename T>
+__global__ void decay_gate_kernel(const T* __restrict__ x, int x_stride, int col0, const float* __restrict__ a_log,
+                                  const float* __restrict__ bias, int per, float* __restrict__ decay,
+                                  float* __restrict__ step, int tokens, int C) {
+  pdl_trigger();
+  pdl_wait();
+  const long long total = static_cast<long long>(tokens) * C;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(idx / C), c = static_cast<int>(idx - static_cast<long long>(t) * C);
+    const float dt = softplus_f(to_float(x[static_cast<size_t>(t) * x_stride + col0 + c]) + (bias ? bias[c] : 0.0f));
+    decay[idx] = expf(-expf(a_log[c / per]) * dt);
+    if (step) step[idx] = dt;
+  }
+}
+
+// ------------------------------------------------------------ unit vectors per head, write strengths
+// Heads of `dim` floats, `heads` of them side by side from column col0 of a float32 row: each becomes
+// x / sqrt(sum(x^2) + eps) times scale_low (heads below `split`) or scale_high.  One warp a head.
+// Beside it, sigmoid of `gates` columns of a row of the engine's dtype into a float32 [T, gates].
+template <typename T>
+__global__ void unit_heads_kernel(float* __restrict__ rows, int stride, int col0, int heads, int dim, float eps,
+                                  int split, float scale_low, float scale_high, const T* __restrict__ gate_in,
+                                  int gate_stride, int gate_col0, int gates, float* __restrict__ gate_out, int tokens) {
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const int t = blockIdx.x;
+  if (t >= tokens) return;
+  for (int head = warp; head < heads; head += warps) {
+    float* v = rows + static_cast<size_t>(t) * stride + col0 + static_cast<size_t>(head) * dim;
+    float sum_sq = 0.0f;
+    for (int i = lane; i < dim; i += 32) sum_sq += v[i] * v[i];
+    sum_sq = warp_sum(sum_sq);
+    const float factor = (head < split ? scale_low : scale_high) / sqrtf(sum_sq + eps);
+    for (int i = lane; i < dim; i += 32) v[i] *= factor;
+  }
+  for (int i = threadIdx.x; i < gates; i += blockDim.x)
+    gate_out[static_cast<size_t>(t) * gates + i] =
+        sigmoid_f(to_float(gate_in[static_cast<size_t>(t) * gate_stride + gate_col0 + i]));
+}
+
+// ------------------------------------------------------------ rotation for heads without a cache
+// in: a row of the engine's dtype with `heads` query heads of `dim` from column q_col0, as many key
+// heads from k_col0 and `heads * vdim` values from v_col0.  out (float32): [q | k | v]; q and k with
+// their first `rot` entries rotated by position (entry i paired with i + rot / 2, angle = position *
+// inv_freq[i], all float32), k times k_scale after the rotation.
+template <typename T>
+__global__ void rotate_heads_kernel(const T* __restrict__ in, int in_stride, int q_col0, int k_col0, int v_col0,
+                                    float* __restrict__ out, const int* __restrict__ positions,
+                                    const float* __restrict__ inv_freq, int heads, int dim, int vdim, int rot,
+                                    float k_scale, int tokens) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  if (t >= tokens) return;
+  const T* row = in + static_cast<size_t>(t) * in_stride;
+  const int qk = heads * dim, half = rot >> 1;
+  float* o = out + static_cast<size_t>(t) * (2 * qk + heads * vdim);
+  const float pos = static_cast<float>(positions[t]);
+  for (int idx = threadIdx.x; idx < 2 * qk; idx += blockDim.x) {
+    const bool is_k = idx >= qk;
+    const int within = is_k ? idx - qk : idx;
+    const int i = within % dim;
+    const T* src = row + (is_k ? k_col0 : q_col0) + (within - i);
+    float v = to_float(src[i]);
+    if (i < rot) {
+      const int pair = i < half ? i : i - half;
+      float s, c;
+      sincosf(pos * inv_freq[pair], &s, &c);
+      v = i < half ? v * c - to_float(src[i + half]) * s : v * c + to_float(src[i - half]) * s;
+    }
+    o[idx] = is_k ? v * k_scale : v;
+  }
+  for (int idx = threadIdx.x; idx < heads * vdim; idx += blockDim.x) o[2 * qk + idx] = to_float(row[v_col0 + idx]);
+}
+
+// ------------------------------------------------------------ the recurrence
+// Per head a state S of dim x vdim floats; per token, in this order:
+//   S <- decay * S                  decay: one number per head (mode 0), per token and head (mode 1),
+//                                   or per token, head and row of S (mode 2)
+//   u = beta * (v - S^T k)          with beta (the delta rule), else u = v_scale * v (v_scale may be null)
+//   S <- S + k u^T
+//   out = S^T q (+ skip * v)
+// Query/key head of head h is h / (heads / kv_heads).
+//
+// A block owns (entry, head, a tile of columns of S) and walks the entry's tokens in order.  A column
+// is shared by `partners` lanes of one warp, each holding kRows consecutive rows of it in registers;
+// sums over rows end in a fixed tree of shuffles.  q, k, row decays, v and the per-token numbers of a
+// run of tokens are staged in shared memory by the whole block, so the walk itself waits on nothing.
+struct ScanArgs {
+  const float* q; int q_stride;
+  const float* k; int k_stride;
+  const float* v; int v_stride;
+  const float* decay; int decay_mode;
+  const float* beta;
+  const float* v_scale;
+  const float* skip;
+  float* out; int out_stride;
+  float* state; long long state_stride; int state_off;
+  const int* cu_seqlens; const int* entry_slot; const int* entry_start;
+  int heads, kv_heads, dim, vdim, slots;
+  int partners, run;
+  int* fault;
+};
+
+constexpr int kScanThreads = 128;
+
+template <int kRows>
+__global__ void __launch_bounds__(kScanThreads) linear_scan_kernel(const ScanArgs a) {
+  extern __shared__ float staged[];
+  pdl_trigger();
+  const int e = blockIdx.x, head = blockIdx.y;
+  const int partners = a.partners, cols_per_warp = 32 / partners;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int part = lane / cols_per_warp, col_in_warp = lane - part * cols_per_warp;
+  const int tile_cols = (kScanThreads / 32) * cols_per_warp;
+  const int col_in_tile = warp * cols_per_warp + col_in_warp;
+  const int col = blockIdx.z * tile_cols + col_in_tile;
+  const bool col_ok = col < a.vdim;
+  const int row0 = part * kRows;
+  const int dim_padded = partners * kRows;
+  const int kv_head = head / (a.heads / a.kv_heads);
+
+  const int first = a.cu_seqlens[e], length = a.cu_seqlens[e + 1] - first, start = a.entry_start[e];
+  int slot = a.entry_slot[e];
+  bool slot_ok = slot >= 0 && slot < a.slots;
+  if (!slot_ok) {
+    if (threadIdx.x == 0) atomicOr(a.fault, kFaultSlot);
+    slot = 0;
+  }
+  float* home = a.state + slot * a.state_stride + a.state_off + static_cast<size_t>(head) * a.dim * a.vdim;
+
+  // shared: k, q (and row decays) [run][dim_padded]; v [run][tile_cols]; beta / v_scale / decay [run] each
+  const int run = a.run;
+  float* sk = staged;
+  float* sq = sk + run * dim_padded;
+  float* sg = sq + run * dim_padded;
+  float* sv = sg + (a.decay_mode == 2 ? run * dim_padded : 0);
+  float* sbeta = sv + run * tile_cols;
+  float* sdecay = sbeta + run;
+
+  pdl_wait();
+  float S[kRows];
+#pragma unroll
+  for (int r = 0; r < kRows; ++r) {
+    const int i = row0 + r;
+    S[r] = (start > 0 && col_ok && i < a.dim) ? home[static_cast<size_t>(i) * a.vdim + col] : 0.0f;
+  }
+  const float fixed_decay = a.decay_mode == 0 ? a.decay[head] : 1.0f;
+  const float skip = a.skip ? a.skip[head] : 0.0f;
+
+  for (int base = 0; base < length; base += run) {
+    const int count = min(run, length - base);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < count * dim_padded; idx += kScanThreads) {
+      const int tt = idx / dim_padded, i = idx - tt * dim_padded;
+      const size_t t = static_cast<size_t>(first + base + tt);
+      const bool in = i < a.dim;
+      sk[idx] = in ? a.k[t * a.k_stride + kv_head * a.dim + i] : 0.0f;
+      sq[idx] = in ? a.q[t * a.q_stride + kv_head * a.dim + i] : 0.0f;
+      if (a.decay_mode == 2) sg[idx] = in ? a.decay[(t * a.heads + head) * a.dim + i] : 1.0f;
+    }
+    for (int idx = threadIdx.x; idx < count * tile_cols; idx += kScanThreads) {
+      const int tt = idx / tile_cols, j = idx - tt * tile_cols;
+      const int c = blockIdx.z * tile_cols + j;
+      sv[idx] = c < a.vdim ? a.v[static_cast<size_t>(first + base + tt) * a.v_stride + head * a.vdim + c] : 0.0f;
+    }
+    for (int tt = threadIdx.x; tt < count; tt += kScanThreads) {
+      const size_t at = static_cast<size_t>(first + base + tt) * a.heads + head;
+      sbeta[tt] = a.beta ? a.beta[at] : (a.v_scale ? a.v_scale[at] : 1.0f);
+      sdecay[tt] = a.decay_mode == 1 ? a.decay[at] : fixed_decay;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < count; ++tt) {
+      const float* kk = sk + tt * dim_padded + row0;
+      const float* qq = sq + tt * dim_padded + row0;
+      const float vj = sv[tt * tile_cols + col_in_tile];
+      if (a.decay_mode == 2) {
+        const float* gg = sg + tt * dim_padded + row0;
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) S[r] *= gg[r];
+      } else {
+        const float d = sdecay[tt];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) S[r] *= d;
+      }
+      float u;
+      if (a.beta) {
+        float seen = 0.0f;
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) seen += S[r] * kk[r];
+        for (int offset = cols_per_warp; offset < 32; offset <<= 1) seen += __shfl_xor_sync(0xffffffffu, seen, offset);
+        u = sbeta[tt] * (vj - seen);
+      } else {
+        u = sbeta[tt] * vj;
+      }
+      float o = 0.0f;
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) {
+        S[r] += kk[r] * u;
+        o += S[r] * qq[r];
+      }
+      for (int offset = cols_per_warp; offset < 32; offset <<= 1) o += __shfl_xor_sync(0xffffffffu, o, offset);
+      if (part == 0 && col_ok)
+        a.out[static_cast<size_t>(first + base + tt) * a.out_stride + head * a.vdim + col] = o + skip * vj;
+    }
+  }
+  if (slot_ok && col_ok) {
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+      const int i = row0 + r;
+      if (i < a.dim) home[static_cast<size_t>(i) * a.vdim + col] = S[r];
+    }
+  }
+}
+
+// ------------------------------------------------------------ norm and gate after a mixer
+// y: [T, C] in groups of `group` columns.  gate = act(g[t, g_col0 + c]) with act 0 none, 1 sigmoid,
+// 2 SiLU.  With `gate_first` the gate multiplies before the norm, else after it.  The norm (if `norm`)
+// divides a group by sqrt(mean(z^2) + eps) and multiplies by weight[c % weight_period] (or nothing).
+// One block per (token, group); float32 arithmetic, one rounding at the store.
+template <typename TY, typename T>
+__global__ void gated_norm_kernel(const TY* __restrict__ y, int y_stride, const T* __restrict__ g, int g_stride,
+                                  int g_col0, int act, int gate_first, int norm, const float* __restrict__ weight,
+                                  int weight_period, float eps, T* __restrict__ out, int group, int groups) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, part = blockIdx.y;
+  const TY* yr = y + static_cast<size_t>(t) * y_stride + static_cast<size_t>(part) * group;
+  const T* gr = g ? g + static_cast<size_t>(t) * g_stride + g_col0 + static_cast<size_t>(part) * group : nullptr;
+  T* o = out + (static_cast<size_t>(t) * groups + part) * group;
+  auto gate_at = [&](int i) {
+    if (!gr || act == 0) return 1.0f;
+    const float raw = to_float(gr[i]);
+    return act == 1 ? sigmoid_f(raw) : silu_f(raw);
+  };
+  float inv = 1.0f;
+  if (norm) {
+    float sum_sq = 0.0f;
+    for (int i = threadIdx.x; i < group; i += blockDim.x) {
+      float z = to_float(yr[i]);
+      if (gate_first) z *= gate_at(i);
+      sum_sq += z * z;
+    }
+    sum_sq = block_sum(sum_sq, scratch);
+    inv = 1.0f / sqrtf(sum_sq / static_cast<float>(group) + eps);
+  }
+  for (int i = threadIdx.x; i < group; i += blockDim.x) {
+    const float gate = gate_at(i);
+    float z = to_float(yr[i]);
+    if (gate_first) z *= gate;
+    z *= inv;
+    if (norm && weight) z *= weight[(part * group + i) % weight_period];
+    if (!gate_first) z *= gate;
+    o[i] = from_float<T>(z);
+  }
+}
+
+// ------------------------------------------------------------ xIELU
+// z > 0: softplus(p) z^2 + z / 2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2;  pq = {p, q}.
+template <typename T>
+__global__ void xielu_kernel(const T* __restrict__ in, T* __restrict__ out, const float* __restrict__ pq, size_t n) {
+  pdl_trigger();
+  const float up = softplus_f(pq[0]), down = 0.5f + softplus_f(pq[1]);
+  pdl_wait();
+  for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < n;
+       idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const float z = to_float(in[idx]);
+    const float r = z > 0.0f ? up * z * z + 0.5f * z : down * (expm1f(z) - z) + 0.5f * z;
+    out[idx] = from_float<T>(r);
+  }
+}
+
+// weighted sum of two results: out = a_scale * a + b_scale * b (float32 arithmetic)
+template <typename T>
+__global__ void scaled_sum_kernel(const T* __restrict__ a, const T* __restrict__ b, float a_scale, float b_scale,
+                                  T* __restrict__ out, size_t n) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < n;
+       idx += static_cast<size_t>(gridDim.x) * blockDim.x)
+    out[idx] = from_float<T>(a_scale * to_float(a[idx]) + b_scale * to_float(b[idx]));
+}
+
+inline unsigned flat_blocks(long long total, int threads) {
+  long long blocks = (total + threads - 1) / threads;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  return static_cast<unsigned>(blocks < 1 ? 1 : blocks);
+}
+
+}  // namespace rl
+
+extern "C" {
+
+// out = silu(conv(x)) for every row of the step, then the slots' tails are brought up to date.
+int rl_causal_conv_silu(int dtype, const void* x, int x_stride, int col0, const float* taps, const float* bias,
+                        float* state, long long state_stride, int state_off, float* out, const int* cu_seqlens,
+                        const int* entry_slot, const int* entry_start, int entries, int tokens, int channels,
+                        int width, int slots, int* fault, int pdl, cudaStream_t stream) {
+  if (tokens == 0 || channels == 0) return 0;
+  if (width < 1 || width > rl::kMaxTaps || entries < 1) return static_cast<int>(cudaErrorInvalidValue);
+  RL_DISPATCH_DTYPE(dtype, {
+    int code = rl::launch_kernel(rl::causal_conv_silu_kernel<scalar_t>,
+                                 dim3(rl::flat_blocks(static_cast<long long>(tokens) * channels, 256)), dim3(256), 0,
+                                 stream, pdl != 0, static_cast<const scalar_t*>(x), x_stride, col0, taps, bias,
+                                 static_cast<const float*>(state), state_stride, state_off, out, cu_seqlens,
+                                 entry_slot, entry_start, entries, tokens, channels, width, slots, fault);
+    if (code != 0 || width == 1) return code;
+    return rl::launch_kernel(rl::conv_tail_update_kernel<scalar_t>,
+                             dim3(rl::flat_blocks(static_cast<long long>(entries) * channels, 256)), dim3(256), 0,
+                             stream, pdl != 0, static_cast<const scalar_t*>(x), x_stride, col0, state, state_stride,
+                             state_off, cu_seqlens, entry_slot, entry_start, entries, channels, width, slots);
+  });
+  return 0;
+}
+
+int rl_decay_gate(int dtype, const void* x, int x_stride, int col0, const float* a_log, const float* bias, int per,
+                  float* decay, float* step, int tokens, int channels, int pdl, cudaStream_t stream) {
+  if (tokens == 0 || channels == 0) return 0;
+  if (per < 1) return static_cast<int>(cudaErrorInvalidValue);
+  RL_DISPATCH_DTYPE(dtype, {
+    return rl::launch_kernel(rl::decay_gate_kernel<scalar_t>,
+                             dim3(rl::flat_blocks(static_cast<long long>(tokens) * channels, 256)), dim3(256), 0, stream,
+                             pdl != 0, static_cast<const scalar_t*>(x), x_stride, col0, a_log, bias, per, decay, step,
+                             tokens, channels);
+  });
+  return 0;
+}
+
+int rl_unit_heads(int dtype, float* rows, int stride, int col0, int heads, int dim, float eps, int split,
+                  float scale_low, float scale_high, const void* gate_in, int gate_stride, int gate_col0, int gates,
+                  float* gate_out, int tokens, int pdl, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  RL_DISPATCH_DTYPE(dtype, {
+    return rl::launch_kernel(rl::unit_heads_kernel<scalar_t>, dim3(tokens), dim3(128), 0, stream, pdl != 0, rows,
+                             stride, col0, heads, dim, eps, split, scale_low, scale_high,
+                             static_cast<const scalar_t*>(gate_in), gate_stride, gate_col0, gates, gate_out, tokens);
+  });
+  return 0;
+}
+
+int rl_rotate_heads(int dtype, const void* in, int in_stride, int q_col0, int k_col0, int v_col0, float* out,
+                    const int* positions, const float* inv_freq, int heads, int dim, int vdim, int rot, float k_scale,
+                    int tokens, int pdl, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  if (rot < 0 || rot > dim || (rot & 1)) return static_cast<int>(cudaErrorInvalidValue);
+  RL_DISPATCH_DTYPE(dtype, {
+    return rl::launch_kernel(rl::rotate_heads_kernel<scalar_t>, dim3(tokens), dim3(256), 0, stream, pdl != 0,
+                             static_cast<const scalar_t*>(in), in_stride, q_col0, k_col0, v_col0, out, positions,
+                             inv_freq, heads, dim, vdim, rot, k_scale, tokens);
+  });
+  return 0;
+}
+
+int rl_linear_scan(const float* q, int q_stride, const float* k, int k_stride, const float* v, int v_stride,
+                   const float* decay, int decay_mode, const float* beta, const float* v_scale, const float* skip,
+                   float* out, int out_stride, float* state, long long state_stride, int state_off,
+                   const int* cu_seqlens, const int* entry_slot, const int* entry_start, int entries, int heads,
+                   int kv_heads, int dim, int vdim, int slots, int* fault, int pdl, cudaStream_t stream) {
+  if (entries == 0) return 0;
+  if (heads < 1 || kv_heads < 1 || heads % kv_heads || dim < 1 || dim > 1024 || vdim < 1 || decay_mode < 0 ||
+      decay_mode > 2 || decay == nullptr)
+    return static_cast<int>(cudaErrorInvalidValue);
+  // rows a lane holds: a quarter of the column where that is at most 32, and then as many lanes a column as it takes
+  int rows = 4;
+  while (rows < 32 && rows * 4 < dim) rows *= 2;
+  int partners = 1;
+  while (partners * rows < dim) partners *= 2;
+  rl::ScanArgs a;
+  a.q = q; a.q_stride = q_stride; a.k = k; a.k_stride = k_stride; a.v = v; a.v_stride = v_stride;
+  a.decay = decay; a.decay_mode = decay_mode; a.beta = beta; a.v_scale = v_scale; a.skip = skip;
+  a.out = out; a.out_stride = out_stride; a.state = state; a.state_stride = state_stride; a.state_off = state_off;
+  a.cu_seqlens = cu_seqlens; a.entry_slot = entry_slot; a.entry_start = entry_start;
+  a.heads = heads; a.kv_heads = kv_heads; a.dim = dim; a.vdim = vdim; a.slots = slots; a.partners = partners;
+  a.fault = fault;
+  const int tile_cols = (rl::kScanThreads / 32) * (32 / partners);
+  const int dim_padded = partners * rows;
+  const int per_token = (decay_mode == 2 ? 3 : 2) * dim_padded + tile_cols + 2;
+  int run = (40 * 1024 / 4) / per_token;
+  a.run = run > 16 ? 16 : (run < 1 ? 1 : run);
+  const size_t smem = static_cast<size_t>(a.run) * per_token * sizeof(float);
+  const dim3 grid(entries, heads, (vdim + tile_cols - 1) / tile_cols), block(rl::kScanThreads);
+  if (rows == 4) return rl::launch_kernel(rl::linear_scan_kernel<4>, grid, block, smem, stream, pdl != 0, a);
+  if (rows == 8) return rl::launch_kernel(rl::linear_scan_kernel<8>, grid, block, smem, stream, pdl != 0, a);
+  if (rows == 16) return rl::launch_kernel(rl::linear_scan_kernel<16>, grid, block, smem, stream, pdl != 0, a);
+  return rl::launch_kernel(rl::linear_scan_kernel<32>, grid, block, smem, stream, pdl != 0, a);
+}
+
+// y_f32: y is float32 whatever the engine's dtype (the result of a recurrence); else y has the engine's dtype.
+int rl_gated_norm(int dtype, int y_f32, const void* y, int y_stride, const void* g, int g_stride, int g_col0, int act,
+                  int gate_first, int norm, const float* weight, int weight_period, float eps, void* out, int tokens,
+                  int group, int groups, int pdl, cudaStream_t stream) {
+  if (tokens == 0 || groups == 0) return 0;
+  if (group < 1 || act < 0 || act > 2 || (weight != nullptr && weight_period < 1))
+    return static_cast<int>(cudaErrorInvalidValue);
+  int threads = 32;
+  while (threads < 256 && threads * 2 <= group) threads *= 2;
+  const dim3 grid(tokens, groups), block(threads);
+  RL_DISPATCH_DTYPE(dtype, {
+    if (y_f32)
+      return rl::launch_kernel(rl::gated_norm_kernel<float, scalar_t>, grid, block, 0, stream, pdl != 0,
+                               static_cast<const float*>(y), y_stride, static_cast<const scalar_t*>(g), g_stride,
+                               g_col0, act, gate_first, norm, weight, weight_period, eps, static_cast<scalar_t*>(out),
+                               group, groups);
+    return rl::launch_kernel(rl::gated_norm_kernel<scalar_t, scalar_t>, grid, block, 0, stream, pdl != 0,
+                             static_cast<const scalar_t*>(y), y_stride, static_cast<const scalar_t*>(g), g_stride,
+                             g_col0, act, gate_first, norm, weight, weight_period, eps, static_cast<scalar_t*>(out),
+                             group, groups);
+  });
+  return 0;
+}
+
+int rl_xielu(int dtype, const void* in, void* out, const float* pq, long long n, int pdl, cudaStream_t stream) {
+  if (n == 0) return 0;
+  RL_DISPATCH_DTYPE(dtype, {
+    return rl::launch_kernel(rl::xielu_kernel<scalar_t>, dim3(rl::flat_blocks(n, 256)), dim3(256), 0, stream, pdl != 0,
+                             static_cast<const scalar_t*>(in), static_cast<scalar_t*>(out), pq, static_cast<size_t>(n));
+  });
+  return 0;
+}
+
+int rl_scaled_sum(int dtype, const void* a, const void* b, float a_scale, float b_scale, void* out, long long n,
+                  int pdl, cudaStream_t stream) {
+  if (n == 0) return 0;
+  RL_DISPATCH_DTYPE(dtype, {
+    return rl::launch_kernel(rl::scaled_sum_kernel<scalar_t>, dim3(rl::flat_blocks(n, 256)), dim3(256), 0, stream,
+                             pdl != 0, static_cast<const scalar_t*>(a), static_cast<const scalar_t*>(b), a_scale,
+                             b_scale, static_cast<scalar_t*>(out), static_cast<size_t>(n));
+  });
+  return 0;
+}
+
+}  // extern "C"

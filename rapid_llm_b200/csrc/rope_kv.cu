@@ -28,6 +28,7 @@ struct RopeArgs {
   void* q_out;              // [tokens, hq, d]
   void* cache;              // layer cache or null
   int tokens, row_width, hq, hkv, d, rotary, max_pos, page_size, num_pages;
+  int norm_size;            // entries the norm's mean is taken over (d, or fewer when the head's tail is padding)
   float eps;
   int* fault;
 };
@@ -124,7 +125,7 @@ __global__ void qk_norm_rope_write_kernel(const RopeArgs a, const int heads_per_
       if (kind != 2) {
         if (kind == 0 ? a.q_weight != nullptr : a.k_weight != nullptr) {
           sum_sq = warp_sum(sum_sq);
-          const float inv_rms = rsqrtf(sum_sq / static_cast<float>(d) + a.eps);
+          const float inv_rms = rsqrtf(sum_sq / static_cast<float>(a.norm_size) + a.eps);
 #pragma unroll
           for (int i = 0; i < kVec; ++i) v[i] = v[i] * inv_rms * (kind == 0 ? qw[i] : kw[i]);
         }
@@ -202,7 +203,7 @@ __global__ void qk_norm_rope_write_kernel(const RopeArgs a, const int heads_per_
     }
     if (w) {
       sum_sq = warp_sum(sum_sq);
-      const float inv_rms = rsqrtf(sum_sq / static_cast<float>(d) + a.eps);
+      const float inv_rms = rsqrtf(sum_sq / static_cast<float>(a.norm_size) + a.eps);
       for (int i = lane; i < d; i += 32) mine[i] = mine[i] * inv_rms * w[i];
     }
     __syncwarp();
@@ -312,7 +313,7 @@ __global__ void __launch_bounds__(kRopeWarps * 32, 8) qk_norm_rope_write_pairs_k
     for (int step = 8; step > 0; step >>= 1) sum_sq += __shfl_xor_sync(0xffffffffu, sum_sq, step);   // within 16 lanes
     const float* weight = kind == 0 ? a.q_weight : (kind == 1 ? a.k_weight : nullptr);
     if (weight != nullptr) {
-      const float inv_rms = rsqrtf(sum_sq / static_cast<float>(kD) + a.eps);
+      const float inv_rms = rsqrtf(sum_sq / static_cast<float>(a.norm_size) + a.eps);
       const float4 w1 = __ldg(reinterpret_cast<const float4*>(weight + at));
       const float4 w2 = __ldg(reinterpret_cast<const float4*>(weight + kHalf + at));
       x1[0] = x1[0] * inv_rms * w1.x; x1[1] = x1[1] * inv_rms * w1.y; x1[2] = x1[2] * inv_rms * w1.z; x1[3] = x1[3] * inv_rms * w1.w;
@@ -350,10 +351,10 @@ extern "C" int rl_qk_norm_rope_write(int dtype, const void* qkv, int row_width, 
                                      const int* positions, const int* kv_dest, void* q_out,
                                      void* cache, int tokens, int hq, int hkv, int d, int rotary,
                                      int max_pos, int page_size, int num_pages, float eps,
-                                     int* fault, int pdl, cudaStream_t stream) {
+                                     int norm_size, int* fault, int pdl, cudaStream_t stream) {
   if (tokens == 0) return 0;
   if (d > rl::kMaxHeadDim || d <= 0 || rotary < 0 || rotary > d || (rotary & 1) ||
-      (kv_dest != nullptr && cache == nullptr))
+      (kv_dest != nullptr && cache == nullptr) || norm_size < 0 || norm_size > d)
     return static_cast<int>(cudaErrorInvalidValue);
   const int heads_per_token = kv_dest ? hq + 2 * hkv : hq;
   rl::RopeArgs a;
@@ -361,7 +362,7 @@ extern "C" int rl_qk_norm_rope_write(int dtype, const void* qkv, int row_width, 
   a.cos_table = cos_table; a.sin_table = sin_table; a.positions = positions; a.kv_dest = kv_dest;
   a.q_out = q_out; a.cache = cache; a.tokens = tokens; a.row_width = row_width; a.hq = hq; a.hkv = hkv;
   a.d = d; a.rotary = rotary; a.max_pos = max_pos; a.page_size = page_size; a.num_pages = num_pages;
-  a.eps = eps; a.fault = fault;
+  a.eps = eps; a.fault = fault; a.norm_size = norm_size > 0 ? norm_size : d;
   // registers when the whole head rotates, a lane's elements are whole vectors and everything is aligned
   const bool aligned = ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
                          reinterpret_cast<uintptr_t>(cache)) & 15) == 0 && row_width % 8 == 0;

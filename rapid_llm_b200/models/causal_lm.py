@@ -12,7 +12,7 @@ import torch
 from ..config.model_spec import ModelSpec
 from ..engine.batch import LayerCache, StepBatch
 from ..ops import gemm
-from ..parts.base import BLOCKS, EMBEDDINGS, HEADS, NORMS, CacheNeed, StateNeed, TensorSpec
+from ..parts.base import BLOCKS, EMBEDDINGS, HEADS, NORMS, CacheNeed, StateNeed, StreamAddend, TensorSpec
 from ..parts.norm import ADD, PLAIN
 
 
@@ -31,6 +31,24 @@ class CausalLM:
         self.head = HEADS.build(spec.head, **context)
         if hasattr(self.head, "tie_to"):
             self.head.tie_to(self.embedding)
+        # a learned row per pass of a looped run of layers, for run orders whose entries open passes
+        self.pass_offset = None if spec.pass_offset is None else EMBEDDINGS.build(spec.pass_offset, **context)
+        if self.device.type == "cuda":
+            self._build_kernels()
+
+    def _build_kernels(self) -> None:
+        """Compile, side by side, the kernel libraries this model's parts say they launch from (each would
+        otherwise be built at its first launch, one after the other)."""
+        from concurrent.futures import ThreadPoolExecutor
+
+        from ..ops import build
+
+        names = {"core"}
+        for layer in self.layers:
+            if hasattr(layer, "uses_libraries"):
+                names |= layer.uses_libraries()
+        with ThreadPoolExecutor(max_workers=len(names)) as pool:
+            list(pool.map(build.build_library, sorted(names)))
 
     # -- weights ----------------------------------------------------------------- #
     def _owners(self):
@@ -40,6 +58,8 @@ class CausalLM:
             yield layer_spec.prefix, layer
         yield self.spec.final_norm_prefix, self.final_norm
         yield self.spec.head_prefix, self.head
+        if self.pass_offset is not None:
+            yield self.spec.pass_offset_prefix, self.pass_offset
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
         """Every checkpoint tensor by full name, in a fixed order."""
@@ -94,13 +114,22 @@ class CausalLM:
     def forward(self, batch: StepBatch, caches: list[LayerCache]) -> torch.Tensor:
         """Logits ``[R, vocab]`` at ``batch.logit_rows``; runs only the tokens of the step."""
         batch.defer_products = True      # the queue is run below, before anything but a kernel reads a result
-        x = self.embedding.forward(batch)
+        x = embedded = self.embedding.forward(batch)
         residual = None
         schedule = self.spec.schedule
         for position, entry in enumerate(schedule):
-            # the norm that the next layer starts with may ride on this layer's last product
-            after = self.layers[schedule[position + 1].layer].leading_norm() if position + 1 < len(schedule) else None
-            x, residual = self.layers[entry.layer].forward(x, residual, batch, caches[position], then_norm=after)
+            # the norm that the next layer starts with may ride on this layer's last product, unless
+            # something joins the stream in between
+            after = None
+            if position + 1 < len(schedule) and schedule[position + 1].pass_index is None:
+                after = self.layers[schedule[position + 1].layer].leading_norm()
+            if entry.pass_index is None:
+                x, residual = self.layers[entry.layer].forward(x, residual, batch, caches[position], then_norm=after)
+            else:
+                addend = StreamAddend(rows=embedded if entry.add_embedding else None,
+                                      vector=self.pass_offset.row(entry.pass_index))
+                x, residual = self.layers[entry.layer].forward(x, residual, batch, caches[position], then_norm=after,
+                                                               addend=addend)
         if batch.num_logit_rows == 0 or not self.final_norm.reads_deferred:
             gemm.flush()
         if batch.num_logit_rows == 0:

@@ -46,6 +46,7 @@ LIBRARIES: dict[str, list[str]] = {
         "sampling.cu",
     ],
     "gemm": ["gemm_bf16.cu", "gemm_chain.cu", "gemm_bf16_pair.cu"],
+    "recurrent": ["recurrent.cu"],
 }
 LIBRARY_FLAGS: dict[str, list[str]] = {}
 

@@ -117,14 +117,14 @@ def core() -> ctypes.CDLL:
     lib = load_library("core")
     if not _SIGNATURES_SET:
         lib.rl_embedding.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
-        lib.rl_add_rmsnorm.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p]
+        lib.rl_add_rmsnorm.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]
         lib.rl_silu_mul.argtypes = [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         lib.rl_scatter_rows.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
         lib.rl_to_float.argtypes = [c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p]
         lib.rl_qk_norm_rope_write.argtypes = [
             c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-            c_float, c_void_p, c_int, c_void_p,
+            c_float, c_int, c_void_p, c_int, c_void_p,
         ]
         lib.rl_attention_generic.argtypes = [
             c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
@@ -189,14 +189,23 @@ def add_rmsnorm(
     mode: int,
     write_residual: bool,
     row_index: torch.Tensor | None = None,
+    extra_rows: torch.Tensor | None = None,
+    extra_vector: torch.Tensor | None = None,
 ) -> torch.Tensor:
     """RMSNorm of ``x`` (mode 0 or 2) or of ``x + residual`` (mode 1), float32 math.
 
     ``residual`` is the float32 residual stream ``[T, H]``; with ``write_residual`` the
     sum is stored back into it.  ``row_index`` (int32) selects the input rows; ``out`` then
-    has one row per index.
+    has one row per index.  ``extra_rows`` (``[T, H]`` of x's dtype) and ``extra_vector``
+    (float32 ``[H]``) are added to the sum, in that order, before it is stored or normed.
     """
-    _need_cuda(x, residual, weight, out, row_index)
+    _need_cuda(x, residual, weight, out, row_index, extra_rows, extra_vector)
+    _contig("extra_rows", extra_rows), _contig("extra_vector", extra_vector)
+    _expect("extra_vector", extra_vector, torch.float32)
+    if extra_rows is not None and (extra_rows.shape != x.shape or extra_rows.dtype != x.dtype):
+        raise KernelError("add_rmsnorm: extra_rows must have the shape and dtype of x")
+    if extra_vector is not None and extra_vector.numel() != x.shape[-1]:
+        raise KernelError("add_rmsnorm: extra_vector must have one entry per column")
     _expect("weight", weight, torch.float32), _expect("residual", residual, torch.float32)
     _expect("row_index", row_index, torch.int32)
     _contig("x", x), _contig("residual", residual), _contig("out", out)
@@ -208,7 +217,8 @@ def add_rmsnorm(
         raise KernelError("add_rmsnorm: residual must have the shape of x")
     _check(
         core().rl_add_rmsnorm(dtype_tag(x.dtype), _ptr(x), _ptr(residual), _ptr(weight), _ptr(out),
-                              _ptr(row_index), rows, hidden, float(eps), mode, int(write_residual), int(PDL), _stream()),
+                              _ptr(row_index), rows, hidden, float(eps), mode, int(write_residual),
+                              _ptr(extra_rows), _ptr(extra_vector), int(PDL), _stream()),
         f"add_rmsnorm(hidden={hidden})",
     )
     return out
@@ -254,8 +264,11 @@ def qk_norm_rope_write(
     kv_dest: torch.Tensor | None = None,
     cache: torch.Tensor | None = None,
     page_size: int = 1,
+    norm_size: int | None = None,
 ) -> torch.Tensor:
     """Per-head q/k RMSNorm, rotation by position, q to ``q_out``, k and v into the pages.
+
+    ``norm_size``: entries of a head the norm's mean is taken over, when the head's tail is padding.
 
     ``qkv`` is ``[T, (Hq + 2 Hkv) D]`` (or ``[T, Hq D]`` when ``kv_dest`` is ``None`` and
     only queries are produced).  ``cache`` is one layer's ``[pages, 2, Hkv, page, D]``;
@@ -285,7 +298,7 @@ def qk_norm_rope_write(
             dtype_tag(qkv.dtype), _ptr(qkv), row_width, _ptr(bias), _ptr(q_weight), _ptr(k_weight),
             _ptr(cos), _ptr(sin), _ptr(positions), _ptr(kv_dest), _ptr(q_out), _ptr(cache), tokens,
             num_heads, num_kv_heads, head_dim, rotary_dim, cos.shape[0], page_size, num_pages,
-            float(eps), _ptr(fault), int(PDL), _stream(),
+            float(eps), int(norm_size or 0), _ptr(fault), int(PDL), _stream(),
         ),
         f"qk_norm_rope_write(head_dim={head_dim})",
     )
@@ -787,6 +800,224 @@ def sample(
         ),
         f"sample(vocab={logits.shape[1]})",
     )
+    return out
+
+
+# ------------------------------------------------------------- mixers with a state of fixed size
+_RECURRENT_SET = False
+
+
+def recurrent() -> ctypes.CDLL:
+    """The library of the recurrent mixers' kernels (``csrc/recurrent.cu``), built at first use."""
+    global _RECURRENT_SET
+    lib = load_library("recurrent")
+    if not _RECURRENT_SET:
+        lib.rl_causal_conv_silu.argtypes = [
+            c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p,
+            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
+        ]
+        lib.rl_decay_gate.argtypes = [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                      c_int, c_int, c_int, c_void_p]
+        lib.rl_unit_heads.argtypes = [c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_float,
+                                      c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p]
+        lib.rl_rotate_heads.argtypes = [c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                        c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p]
+        lib.rl_linear_scan.argtypes = [
+            c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+            c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+            c_int, c_int, c_void_p, c_int, c_void_p,
+        ]
+        lib.rl_gated_norm.argtypes = [c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                      c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        lib.rl_xielu.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p]
+        lib.rl_scaled_sum.argtypes = [c_int, c_void_p, c_void_p, c_float, c_float, c_void_p, c_longlong, c_int, c_void_p]
+        for name in ("rl_causal_conv_silu", "rl_decay_gate", "rl_unit_heads", "rl_rotate_heads", "rl_linear_scan",
+                     "rl_gated_norm", "rl_xielu", "rl_scaled_sum"):
+            getattr(lib, name).restype = c_int
+        _RECURRENT_SET = True
+    return lib
+
+
+def _row_stride(name: str, tensor: torch.Tensor) -> int:
+    """Row length of a 2-D tensor whose columns are contiguous (a view of some columns is fine)."""
+    if tensor.dim() != 2 or (tensor.shape[1] > 1 and tensor.stride(1) != 1):
+        raise KernelError(f"{name} must be rows of contiguous columns")
+    return tensor.stride(0)
+
+
+def _state_row(state: torch.Tensor) -> tuple[int, int]:
+    """Slots and row stride of a per-slot float32 state ``[slots, n]`` (a view of some columns is fine)."""
+    _expect("state", state, torch.float32)
+    return state.shape[0], _row_stride("state", state)
+
+
+def causal_conv_silu(x: torch.Tensor, taps: torch.Tensor, bias: torch.Tensor | None, tail: torch.Tensor,
+                     out: torch.Tensor, batch) -> torch.Tensor:
+    """``out[t, c] = silu(bias[c] + sum_d taps[c, K - 1 - d] * x[t - d, c])`` over each request's own tokens.
+
+    ``x`` is ``[T, C]`` (a view of columns of the step's rows), ``taps`` float32 ``[C, K]`` with the current
+    token's tap last, ``tail`` float32 ``[slots, (K - 1) * C]``: every slot's last ``K - 1`` inputs, oldest
+    first, read for the tokens before this step and brought up to date afterwards.  ``out`` is float32.
+    """
+    _need_cuda(x, taps, bias, tail, out)
+    _expect("taps", taps, torch.float32), _expect("bias", bias, torch.float32), _expect("out", out, torch.float32)
+    _contig("taps", taps), _contig("out", out)
+    tokens, channels = x.shape
+    width = taps.shape[1]
+    slots, stride = _state_row(tail)
+    if taps.shape[0] != channels or out.shape != (tokens, channels) or tail.shape[1] != (width - 1) * channels:
+        raise KernelError("causal_conv_silu: shapes of x, taps, tail and out do not agree")
+    _check(
+        recurrent().rl_causal_conv_silu(
+            dtype_tag(x.dtype), _ptr(x), _row_stride("x", x), 0, _ptr(taps), _ptr(bias), _ptr(tail), stride, 0,
+            _ptr(out), _ptr(batch.cu_seqlens), _ptr(batch.entry_slot), _ptr(batch.entry_start), batch.num_entries,
+            tokens, channels, width, slots, _ptr(batch.fault), int(PDL), _stream()),
+        f"causal_conv_silu(width={width})",
+    )
+    return out
+
+
+def decay_gate(x: torch.Tensor, a_log: torch.Tensor, bias: torch.Tensor | None, per: int, decay: torch.Tensor,
+               step: torch.Tensor | None = None) -> torch.Tensor:
+    """``step = softplus(x + bias)``, ``decay = exp(-exp(a_log[c // per]) * step)``; float32 results ``[T, C]``."""
+    _need_cuda(x, a_log, bias, decay, step)
+    for name, tensor in (("a_log", a_log), ("bias", bias), ("decay", decay), ("step", step)):
+        _expect(name, tensor, torch.float32), _contig(name, tensor)
+    tokens, channels = x.shape
+    if decay.shape != (tokens, channels) or (step is not None and step.shape != decay.shape) \
+            or a_log.numel() * per != channels or (bias is not None and bias.numel() != channels):
+        raise KernelError("decay_gate: shapes do not agree")
+    _check(recurrent().rl_decay_gate(dtype_tag(x.dtype), _ptr(x), _row_stride("x", x), 0, _ptr(a_log), _ptr(bias),
+                                     int(per), _ptr(decay), _ptr(step), tokens, channels, int(PDL), _stream()), "decay_gate")
+    return decay
+
+
+def unit_heads(rows: torch.Tensor, *, heads: int, dim: int, eps: float, split: int, scale_low: float,
+               scale_high: float, gate_in: torch.Tensor | None = None, gate_out: torch.Tensor | None = None) -> None:
+    """In place on float32 ``rows [T, heads * dim]`` (a view of columns): every head becomes
+    ``x / sqrt(sum(x^2) + eps)`` times ``scale_low`` (heads below ``split``) or ``scale_high``.  With
+    ``gate_in [T, n]`` (engine dtype) also ``gate_out = sigmoid(gate_in)`` as float32 ``[T, n]``."""
+    _need_cuda(rows, gate_in, gate_out)
+    _expect("rows", rows, torch.float32), _expect("gate_out", gate_out, torch.float32), _contig("gate_out", gate_out)
+    tokens = rows.shape[0]
+    if rows.shape[1] != heads * dim:
+        raise KernelError("unit_heads: rows do not hold heads * dim columns")
+    gates = 0 if gate_in is None else gate_in.shape[1]
+    tag = dtype_tag(gate_in.dtype) if gate_in is not None else F32
+    _check(recurrent().rl_unit_heads(tag, _ptr(rows), _row_stride("rows", rows), 0, heads, dim, float(eps), int(split),
+                                     float(scale_low), float(scale_high), _ptr(gate_in),
+                                     0 if gate_in is None else _row_stride("gate_in", gate_in), 0, gates,
+                                     _ptr(gate_out), tokens, int(PDL), _stream()), "unit_heads")
+
+
+def rotate_heads(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
+                 inv_freq: torch.Tensor, *, heads: int, dim: int, vdim: int, k_scale: float) -> torch.Tensor:
+    """``out = [rotated q | rotated k * k_scale | v]`` in float32 from views ``q``, ``k``, ``v`` of columns of
+    one buffer of rows; the first ``2 * len(inv_freq)`` entries of each head rotate (entry i with i + half)."""
+    _need_cuda(q, k, v, out, positions, inv_freq)
+    _expect("out", out, torch.float32), _expect("inv_freq", inv_freq, torch.float32), _expect("positions", positions, torch.int32)
+    _contig("out", out)
+    tokens = q.shape[0]
+    stride = _row_stride("q", q)
+    if _row_stride("k", k) != stride or _row_stride("v", v) != stride or q.dtype != k.dtype or q.dtype != v.dtype:
+        raise KernelError("rotate_heads: q, k and v must be columns of the same rows")
+    if q.shape[1] != heads * dim or k.shape[1] != heads * dim or v.shape[1] != heads * vdim \
+            or out.shape != (tokens, 2 * heads * dim + heads * vdim):
+        raise KernelError("rotate_heads: shapes do not agree")
+    size = q.element_size()
+    _check(recurrent().rl_rotate_heads(
+        dtype_tag(q.dtype), _ptr(q), stride, 0, (k.data_ptr() - q.data_ptr()) // size, (v.data_ptr() - q.data_ptr()) // size,
+        _ptr(out), _ptr(positions), _ptr(inv_freq), heads, dim, vdim, 2 * inv_freq.numel(), float(k_scale), tokens,
+        int(PDL), _stream()), "rotate_heads")
+    return out
+
+
+def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, out: torch.Tensor,
+                state: torch.Tensor, batch, *, heads: int, kv_heads: int, dim: int, vdim: int,
+                beta: torch.Tensor | None = None, v_scale: torch.Tensor | None = None,
+                skip: torch.Tensor | None = None) -> torch.Tensor:
+    """The recurrence ``S <- decay * S; u = beta * (v - S^T k)`` (or ``v_scale * v`` without ``beta``);
+    ``S <- S + k u^T; out = S^T q + skip * v`` per head over every entry's tokens, from and into
+    ``state [slots, heads * dim * vdim]`` (float32; a request at position 0 starts from zeros).
+
+    All operands float32: ``q``, ``k`` ``[T, kv_heads * dim]`` and ``v`` ``[T, heads * vdim]`` (views of columns
+    are fine), ``decay`` ``[heads]`` (fixed), ``[T, heads]`` or ``[T, heads * dim]`` (one per row of ``S``),
+    ``beta``/``v_scale`` ``[T, heads]``, ``skip`` ``[heads]``, ``out`` ``[T, heads * vdim]``.
+    """
+    _need_cuda(q, k, v, decay, out, state, beta, v_scale, skip)
+    for name, tensor in (("q", q), ("k", k), ("v", v), ("decay", decay), ("out", out), ("beta", beta),
+                         ("v_scale", v_scale), ("skip", skip)):
+        _expect(name, tensor, torch.float32)
+    _contig("decay", decay), _contig("beta", beta), _contig("v_scale", v_scale), _contig("skip", skip)
+    tokens = q.shape[0]
+    if q.shape[1] != kv_heads * dim or k.shape != q.shape or v.shape != (tokens, heads * vdim) or out.shape != v.shape:
+        raise KernelError("linear_scan: shapes of q, k, v and out do not agree")
+    if decay.dim() == 1 and decay.numel() == heads:
+        mode = 0
+    elif decay.shape == (tokens, heads):
+        mode = 1
+    elif decay.shape == (tokens, heads * dim):
+        mode = 2
+    else:
+        raise KernelError("linear_scan: decay must be [heads], [T, heads] or [T, heads * dim]")
+    slots, stride = _state_row(state)
+    if state.shape[1] != heads * dim * vdim:
+        raise KernelError("linear_scan: state must hold heads * dim * vdim floats a slot")
+    _check(
+        recurrent().rl_linear_scan(
+            _ptr(q), _row_stride("q", q), _ptr(k), _row_stride("k", k), _ptr(v), _row_stride("v", v), _ptr(decay), mode,
+            _ptr(beta), _ptr(v_scale), _ptr(skip), _ptr(out), _row_stride("out", out), _ptr(state), stride, 0,
+            _ptr(batch.cu_seqlens), _ptr(batch.entry_slot), _ptr(batch.entry_start), batch.num_entries, heads, kv_heads,
+            dim, vdim, slots, _ptr(batch.fault), int(PDL), _stream()),
+        f"linear_scan(dim={dim}, vdim={vdim})",
+    )
+    return out
+
+
+GATE_NONE, GATE_SIGMOID, GATE_SILU = 0, 1, 2
+
+
+def gated_norm(y: torch.Tensor, out: torch.Tensor, *, group: int, gate: torch.Tensor | None = None,
+               act: int = GATE_NONE, gate_first: bool = False, norm: bool = True, weight: torch.Tensor | None = None,
+               eps: float = 0.0) -> torch.Tensor:
+    """Norm and gate of a mixer's result: ``y [T, C]`` (float32, or the engine's dtype) in groups of ``group``
+    columns, each divided by ``sqrt(mean(z^2) + eps)`` and multiplied by ``weight[c % len(weight)]``; the gate
+    ``act(gate[t, c])`` multiplies before (``gate_first``) or after the norm.  ``out`` has the engine's dtype."""
+    _need_cuda(y, out, gate, weight)
+    _expect("weight", weight, torch.float32), _contig("weight", weight), _contig("out", out)
+    tokens, width = y.shape
+    if width % group or out.shape != y.shape or (gate is not None and (gate.shape != y.shape or gate.dtype != out.dtype)):
+        raise KernelError("gated_norm: shapes do not agree")
+    if y.dtype != torch.float32 and y.dtype != out.dtype:
+        raise KernelError("gated_norm: y must be float32 or of out's dtype")
+    _check(
+        recurrent().rl_gated_norm(
+            dtype_tag(out.dtype), int(y.dtype == torch.float32), _ptr(y), _row_stride("y", y), _ptr(gate),
+            0 if gate is None else _row_stride("gate", gate), 0, int(act), int(gate_first), int(norm), _ptr(weight),
+            0 if weight is None else weight.numel(), float(eps), _ptr(out), tokens, group, width // group, int(PDL), _stream()),
+        "gated_norm",
+    )
+    return out
+
+
+def xielu(x: torch.Tensor, out: torch.Tensor, pq: torch.Tensor) -> torch.Tensor:
+    """``z > 0: softplus(p) z^2 + z / 2``; ``z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2``; ``pq = [p, q]``."""
+    _need_cuda(x, out, pq)
+    _contig("x", x), _contig("out", out), _expect("pq", pq, torch.float32)
+    if out.shape != x.shape or out.dtype != x.dtype or pq.numel() != 2:
+        raise KernelError("xielu: shapes do not agree")
+    _check(recurrent().rl_xielu(dtype_tag(x.dtype), _ptr(x), _ptr(out), _ptr(pq), x.numel(), int(PDL), _stream()), "xielu")
+    return out
+
+
+def scaled_sum(a: torch.Tensor, b: torch.Tensor, a_scale: float, b_scale: float, out: torch.Tensor) -> torch.Tensor:
+    """``out = a_scale * a + b_scale * b`` (float32 arithmetic)."""
+    _need_cuda(a, b, out)
+    _contig("a", a), _contig("b", b), _contig("out", out)
+    if a.shape != b.shape or out.shape != a.shape or a.dtype != b.dtype or out.dtype != a.dtype:
+        raise KernelError("scaled_sum: shapes do not agree")
+    _check(recurrent().rl_scaled_sum(dtype_tag(a.dtype), _ptr(a), _ptr(b), float(a_scale), float(b_scale), _ptr(out),
+                                     a.numel(), int(PDL), _stream()), "scaled_sum")
     return out
 
 

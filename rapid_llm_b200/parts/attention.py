@@ -12,6 +12,14 @@ normed differ per layer if the specification says so, and so does ``qkv_bias`` (
 q, k and v projections, which this architecture does not have and its predecessor has; added in
 float32 in the product's epilogue).  A layer that reads another entry's
 cache (``cache.writes`` false) projects queries only.
+
+Two more options serve architectures beside the reference's: a value size that differs from the
+query/key size (``value_dim``), and an output gate (``gate="sigmoid"``: the concatenated heads are
+multiplied by ``sigmoid(W_g x)`` before the output projection).  The kernels and the cache keep one
+head size for keys and values, a multiple of 16: where the two sizes differ, or are no such multiple,
+every head is laid out in the larger one rounded up, with zero weight rows (and zero columns of the
+output projection) for the padding, which changes no score and no output; the q/k norm's mean is
+taken over the true size.  ``names`` maps the tensors' default names to an architecture's own.
 """
 
 from __future__ import annotations
@@ -174,19 +182,35 @@ class GQAAttention(Mixer):
         scale: float | None = None,
         shares_cache: bool = False,
         qkv_bias: bool = False,
+        value_dim: int | None = None,
+        gate: str | None = None,
+        names: dict[str, str] | None = None,
         dtype,
         device,
     ) -> None:
         super().__init__(dtype=dtype, device=device)
         if num_heads % num_kv_heads:
             raise ValueError(f"num_heads ({num_heads}) must be divisible by num_kv_heads ({num_kv_heads})")
-        if head_dim % 16 or head_dim > 256:
-            raise ValueError(f"head_dim ({head_dim}) must be a multiple of 16 up to 256")
+        # true sizes of a query/key head and of a value head, and the one size both are laid out in
+        self.qk_dim = int(head_dim)
+        self.v_dim = int(value_dim) if value_dim is not None else self.qk_dim
+        padded = -(-max(self.qk_dim, self.v_dim) // 16) * 16
+        if min(self.qk_dim, self.v_dim) < 1 or padded > 256:
+            raise ValueError(f"head sizes ({head_dim}, {value_dim}) must lie between 1 and 256")
+        if gate not in (None, "sigmoid"):
+            raise ValueError(f"unknown output gate {gate!r}")
+        if (qkv_bias or shares_cache) and (padded != self.qk_dim or padded != self.v_dim):
+            raise ValueError("padded head sizes are not combined with a bias or a shared cache")
+        self.gate = gate
+        self.names = {name: name for name in (
+            "q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight", "q_proj.bias", "k_proj.bias",
+            "v_proj.bias", "q_norm.weight", "k_norm.weight", "g_proj.weight")}
+        self.names.update(names or {})
         self.hidden = int(hidden_size)
-        self.hq, self.hkv, self.d = int(num_heads), int(num_kv_heads), int(head_dim)
+        self.hq, self.hkv, self.d = int(num_heads), int(num_kv_heads), padded
         self.qk_norm, self.eps = bool(qk_norm), float(qk_norm_eps)
         self.window = int(window)
-        self.scale = float(scale) if scale is not None else self.d**-0.5
+        self.scale = float(scale) if scale is not None else self.qk_dim**-0.5
         self.shares_cache = bool(shares_cache)
         device = torch.device(device)
         sms = torch.cuda.get_device_properties(device).multi_processor_count if device.type == "cuda" else DEFAULT_SMS
@@ -195,7 +219,7 @@ class GQAAttention(Mixer):
             clusters = kernels.attention_decode_clusters(self.d, device) or None
         self._items = AttentionItems(self.hq // self.hkv, self.hkv, self.d, sms, clusters)
         self.position = POSITION_ENCODINGS.build(position, dtype=dtype, device=device)
-        self.rotary_dim = int(position.params.get("rotary_dim", self.d))
+        self.rotary_dim = int(getattr(self.position, "rotary_dim", self.d))
 
         kv_rows = 0 if self.shares_cache else 2 * self.hkv * self.d
         self.qkv = self.new_storage((self.hq * self.d + kv_rows, self.hidden), MATRIX)
@@ -203,6 +227,7 @@ class GQAAttention(Mixer):
         self.qkv_bias = self.new_storage((self.qkv.shape[0],), VECTOR) if qkv_bias else None
         self.q_norm = self.new_storage((self.d,), VECTOR) if self.qk_norm else None
         self.k_norm = self.new_storage((self.d,), VECTOR) if self.qk_norm and not self.shares_cache else None
+        self.g = self.new_storage((self.hq * self.d, self.hidden), MATRIX) if self.gate else None
 
     # -- needs ----------------------------------------------------------------- #
     def cache_need(self) -> CacheNeed | None:
@@ -217,31 +242,43 @@ class GQAAttention(Mixer):
     # -- weights --------------------------------------------------------------- #
     def tensor_specs(self) -> dict[str, TensorSpec]:
         specs = {
-            "q_proj.weight": TensorSpec((self.hq * self.d, self.hidden)),
-            "o_proj.weight": TensorSpec((self.hidden, self.hq * self.d)),
+            "q_proj.weight": TensorSpec((self.hq * self.qk_dim, self.hidden)),
+            "o_proj.weight": TensorSpec((self.hidden, self.hq * self.v_dim)),
         }
         if not self.shares_cache:
-            specs["k_proj.weight"] = TensorSpec((self.hkv * self.d, self.hidden))
-            specs["v_proj.weight"] = TensorSpec((self.hkv * self.d, self.hidden))
+            specs["k_proj.weight"] = TensorSpec((self.hkv * self.qk_dim, self.hidden))
+            specs["v_proj.weight"] = TensorSpec((self.hkv * self.v_dim, self.hidden))
         if self.qkv_bias is not None:
             for name in ("q_proj", "k_proj", "v_proj")[: 1 if self.shares_cache else 3]:
                 specs[f"{name}.bias"] = TensorSpec((specs[f"{name}.weight"].shape[0],), VECTOR)
         if self.qk_norm:
-            specs["q_norm.weight"] = TensorSpec((self.d,), VECTOR, init="ones_normal")
+            specs["q_norm.weight"] = TensorSpec((self.qk_dim,), VECTOR, init="ones_normal")
             if not self.shares_cache:
-                specs["k_norm.weight"] = TensorSpec((self.d,), VECTOR, init="ones_normal")
-        return specs
+                specs["k_norm.weight"] = TensorSpec((self.qk_dim,), VECTOR, init="ones_normal")
+        if self.gate:
+            specs["g_proj.weight"] = TensorSpec((self.hq * self.v_dim, self.hidden))
+        return {self.names[name]: spec for name, spec in specs.items()}
+
+    def _heads(self, rows: torch.Tensor, heads: int) -> torch.Tensor:
+        """``rows [heads * d, n]`` as ``[heads, d, n]``: a head's true rows come first, padding after."""
+        return rows.view(heads, self.d, rows.shape[1])
 
     def load_tensor(self, name: str, tensor: torch.Tensor) -> None:
         q_rows, kv_rows = self.hq * self.d, self.hkv * self.d
+        name = {theirs: ours for ours, theirs in self.names.items()}.get(name, "")
         if name == "q_proj.weight":
-            self.qkv[:q_rows].copy_(tensor)
+            self._heads(self.qkv[:q_rows], self.hq)[:, : self.qk_dim].copy_(tensor.view(self.hq, self.qk_dim, -1))
         elif name == "k_proj.weight":
-            self.qkv[q_rows : q_rows + kv_rows].copy_(tensor)
+            self._heads(self.qkv[q_rows : q_rows + kv_rows], self.hkv)[:, : self.qk_dim].copy_(
+                tensor.view(self.hkv, self.qk_dim, -1))
         elif name == "v_proj.weight":
-            self.qkv[q_rows + kv_rows :].copy_(tensor)
+            self._heads(self.qkv[q_rows + kv_rows :], self.hkv)[:, : self.v_dim].copy_(
+                tensor.view(self.hkv, self.v_dim, -1))
         elif name == "o_proj.weight":
-            self.o.copy_(tensor)
+            self.o.view(self.hidden, self.hq, self.d)[:, :, : self.v_dim].copy_(
+                tensor.view(self.hidden, self.hq, self.v_dim))
+        elif name == "g_proj.weight":
+            self._heads(self.g, self.hq)[:, : self.v_dim].copy_(tensor.view(self.hq, self.v_dim, -1))
         elif name == "q_proj.bias":
             self.qkv_bias[:q_rows].copy_(tensor.to(torch.float32))
         elif name == "k_proj.bias":
@@ -249,21 +286,29 @@ class GQAAttention(Mixer):
         elif name == "v_proj.bias":
             self.qkv_bias[q_rows + kv_rows :].copy_(tensor.to(torch.float32))
         elif name == "q_norm.weight":
-            self.q_norm.copy_(tensor.to(torch.float32))
+            self.q_norm[: self.qk_dim].copy_(tensor.to(torch.float32))
         elif name == "k_norm.weight":
-            self.k_norm.copy_(tensor.to(torch.float32))
+            self.k_norm[: self.qk_dim].copy_(tensor.to(torch.float32))
         else:
             raise KeyError(name)
 
     def parameter_bytes(self) -> int:
-        total = (self.qkv.numel() + self.o.numel()) * self.qkv.element_size()
+        total = (self.qkv.numel() + self.o.numel() + (0 if self.g is None else self.g.numel())) * self.qkv.element_size()
         for vector in (self.q_norm, self.k_norm, self.qkv_bias):
             if vector is not None:
                 total += vector.numel() * 4
         return total
 
     def workspace_elements_per_token(self) -> int:
-        return self.qkv.shape[0] + 2 * self.hq * self.d + self.hidden      # qkv, q, attended, projected
+        gate = 2 * self.hq * self.d if self.gate else 0
+        return self.qkv.shape[0] + 2 * self.hq * self.d + self.hidden + gate      # qkv, q, attended, projected
+
+    def uses_libraries(self) -> set[str]:
+        found = {"recurrent"} if self.gate else set()
+        if self.dtype == torch.bfloat16:
+            from ..ops.build import attention_library
+            found |= {"gemm", attention_library(self.d)}
+        return found
 
     # -- forward --------------------------------------------------------------- #
     def forward(self, x, batch, cache, then_norm=None):
@@ -284,10 +329,16 @@ class GQAAttention(Mixer):
             q_weight=self.q_norm, k_weight=self.k_norm,
             kv_dest=group.kv_dest if cache.writes else None,
             cache=cache.pages if cache.writes else None,
-            page_size=group.page_size,
+            page_size=group.page_size, norm_size=self.qk_dim,
         )
         attended = batch.workspace.get("attn_out", rows, self.hq * self.d, x.dtype)
         self.attend(q, cache.pages, attended, batch, group)
+        if self.gate:
+            gate = batch.workspace.get("attn_gate", rows, self.hq * self.d, x.dtype)
+            gemm.linear(x, self.g, gate, batch.fault)
+            gated = batch.workspace.get("attn_gated", rows, self.hq * self.d, x.dtype)
+            attended = kernels.gated_norm(attended, gated, group=self.hq * self.d, gate=gate,
+                                          act=kernels.GATE_SIGMOID, norm=False)
         out = batch.workspace.get("attn_proj", rows, self.hidden, x.dtype)
         return gemm.linear(attended, self.o, out, batch.fault, then_norm=then_norm, defer=batch.defer_products)
 

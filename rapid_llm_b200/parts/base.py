@@ -95,6 +95,16 @@ class StateNeed:
     dtype: torch.dtype
 
 
+@dataclass
+class StreamAddend:
+    """What a model feeds into the residual stream right before a layer: ``rows`` (a row per token of the
+    step, the engine's dtype) and ``vector`` (float32, the same for every token), either may be ``None``.
+    The layer's first norm adds them, in that order, to the float32 sum it forms anyway."""
+
+    rows: torch.Tensor | None = None
+    vector: torch.Tensor | None = None
+
+
 @dataclass(frozen=True)
 class StepShape:
     """What the host knows about a step before it runs, for parts that plan work on the host.
@@ -149,6 +159,11 @@ class Part:
 
     def parameter_bytes(self) -> int:
         return 0
+
+    def uses_libraries(self) -> set[str]:
+        """Kernel libraries of :mod:`rapid_llm_b200.ops.build` this part launches from, beyond the core one
+        (so that a model can have them built before its first step)."""
+        return set()
 
     def workspace_elements_per_token(self) -> int:
         """Elements of the engine dtype this part's activation buffers hold per token of a step
@@ -232,9 +247,11 @@ class Block(Part):
         (``ops.gemm.ScaledRows``) as ``x`` from the block before it."""
         return None
 
-    def forward(self, x, residual, batch, cache, then_norm=None):
+    def forward(self, x, residual, batch, cache, then_norm=None, addend=None):
         """``then_norm``: the next block's :meth:`leading_norm`, which this block's last product may
-        take along (it then returns ``ScaledRows`` as ``x`` and the residual already holds the sum)."""
+        take along (it then returns ``ScaledRows`` as ``x`` and the residual already holds the sum).
+        ``addend`` (:class:`StreamAddend`) is passed only by a run order that has one for this entry: it
+        joins the stream before the block's first norm."""
         raise NotImplementedError
 
 

@@ -36,19 +36,21 @@ class PreNormBlock(Block):
     def __init__(self, *, layer: LayerSpec, dtype, device, names: dict[str, str] | None = None) -> None:
         super().__init__(dtype=dtype, device=device)
         self.names = dict(self.NAMES)
-        self.names.update(names or {})
+        self.names.update(names or layer.names or {})
         self.mixer_norm = NORMS.build(layer.norm, dtype=dtype, device=device)
         self.mixer = MIXERS.build(layer.mixer, dtype=dtype, device=device)
-        self.feed_forward_norm = NORMS.build(layer.norm, dtype=dtype, device=device)
-        self.feed_forward = FEED_FORWARDS.build(layer.feed_forward, dtype=dtype, device=device)
+        # a layer without a feed-forward is the mixer's half alone: x + Mixer(Norm(x))
+        self.feed_forward_norm = self.feed_forward = None
+        if layer.feed_forward is not None:
+            self.feed_forward_norm = NORMS.build(layer.norm, dtype=dtype, device=device)
+            self.feed_forward = FEED_FORWARDS.build(layer.feed_forward, dtype=dtype, device=device)
 
     def _children(self):
-        return (
-            (self.names["mixer_norm"], self.mixer_norm),
-            (self.names["mixer"], self.mixer),
-            (self.names["feed_forward_norm"], self.feed_forward_norm),
-            (self.names["feed_forward"], self.feed_forward),
-        )
+        children = [(self.names["mixer_norm"], self.mixer_norm), (self.names["mixer"], self.mixer)]
+        if self.feed_forward is not None:
+            children += [(self.names["feed_forward_norm"], self.feed_forward_norm),
+                         (self.names["feed_forward"], self.feed_forward)]
+        return tuple(children)
 
     def cache_need(self):
         return self.mixer.cache_need()
@@ -59,6 +61,12 @@ class PreNormBlock(Block):
     def step_planners(self):
         planner = self.mixer.step_planner()
         return [] if planner is None else [planner]
+
+    def uses_libraries(self) -> set[str]:
+        found: set[str] = set()
+        for _, part in self._children():
+            found |= part.uses_libraries()
+        return found
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
         specs = {}
@@ -87,17 +95,25 @@ class PreNormBlock(Block):
     def leading_norm(self):
         return self.mixer_norm if self.mixer.rides_norms else None
 
-    def forward(self, x, residual, batch, cache, then_norm=None):
+    def forward(self, x, residual, batch, cache, then_norm=None, addend=None):
         """``(x, residual)`` in, ``(x, residual)`` out; ``residual`` is ``None`` for the first layer."""
         if not self.mixer_norm.reads_deferred:
             gemm.flush()        # a norm that is no kernel of ops.kernels reads finished results only
+        extra = {} if addend is None else {"addend": addend}
         if isinstance(x, ScaledRows):
+            if addend is not None:
+                raise ValueError("a norm that rode on the product before it cannot take an addend")
             normed = x          # the block before took this block's first norm along
         elif residual is None:
             residual = batch.workspace.get("residual", x.shape[0], x.shape[1], torch.float32)
-            normed = self.mixer_norm.forward(x, residual, batch, mode=FIRST, write_residual=True)
+            normed = self.mixer_norm.forward(x, residual, batch, mode=FIRST, write_residual=True, **extra)
         else:
-            normed = self.mixer_norm.forward(x, residual, batch, mode=ADD, write_residual=True)
+            normed = self.mixer_norm.forward(x, residual, batch, mode=ADD, write_residual=True, **extra)
+        if self.feed_forward is None:
+            if self.mixer.rides_norms:
+                offer = then_norm.following(residual, batch) if then_norm is not None else None
+                return self.mixer.forward(normed, batch, cache, then_norm=offer), residual
+            return self.mixer.forward(normed, batch, cache), residual
         if self.mixer.rides_norms:
             offer = self.feed_forward_norm.following(residual, batch) if self.feed_forward.rides_norms else None
             mixed = self.mixer.forward(normed, batch, cache, then_norm=offer)

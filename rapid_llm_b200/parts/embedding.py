@@ -12,21 +12,22 @@ from __future__ import annotations
 import torch
 
 from ..ops import gemm, kernels
-from .base import EMBEDDINGS, HEADS, MATRIX, Part, TensorSpec
+from .base import EMBEDDINGS, HEADS, MATRIX, VECTOR, Part, TensorSpec
 
 
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Part):
-    def __init__(self, *, vocab_size: int, hidden_size: int, dtype, device) -> None:
+    def __init__(self, *, vocab_size: int, hidden_size: int, dtype, device, name: str = "weight") -> None:
         super().__init__(dtype=dtype, device=device)
         self.vocab, self.hidden = int(vocab_size), int(hidden_size)
+        self.name = name          # the tensor's name after the part's prefix (may be empty)
         self.weight = self.new_storage((self.vocab, self.hidden), MATRIX)
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
-        return {"weight": TensorSpec((self.vocab, self.hidden))}
+        return {self.name: TensorSpec((self.vocab, self.hidden))}
 
     def load_tensor(self, name: str, tensor: torch.Tensor) -> None:
-        if name != "weight":
+        if name != self.name:
             raise KeyError(name)
         self.weight.copy_(tensor)
 
@@ -36,6 +37,31 @@ class TokenEmbedding(Part):
     def forward(self, batch) -> torch.Tensor:
         out = batch.workspace.get("embedded", batch.num_tokens, self.hidden, self.dtype)
         return kernels.embedding(out, self.weight, batch.token_ids, batch.fault, batch.feedback)
+
+
+@EMBEDDINGS.register("pass_offset")
+class PassOffset(Part):
+    """A learned row per pass over a looped run of layers, ``[passes, hidden]``: row ``t`` joins the residual
+    stream (a float32 sum) right before the first layer of pass ``t``; kept in float32."""
+
+    def __init__(self, *, passes: int, hidden_size: int, dtype, device, name: str = "step") -> None:
+        super().__init__(dtype=dtype, device=device)
+        self.passes, self.hidden, self.name = int(passes), int(hidden_size), name
+        self.weight = self.new_storage((self.passes, self.hidden), VECTOR)
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        return {self.name: TensorSpec((self.passes, self.hidden), VECTOR)}
+
+    def load_tensor(self, name: str, tensor: torch.Tensor) -> None:
+        if name != self.name:
+            raise KeyError(name)
+        self.weight.copy_(tensor.to(torch.float32))
+
+    def parameter_bytes(self) -> int:
+        return self.weight.numel() * 4
+
+    def row(self, index: int) -> torch.Tensor:
+        return self.weight[index]
 
 
 @HEADS.register("lm_head")

@@ -10,8 +10,8 @@ from __future__ import annotations
 
 import torch
 
-from ..ops import gemm
-from .base import FEED_FORWARDS, MATRIX, FeedForward, TensorSpec
+from ..ops import gemm, kernels
+from .base import FEED_FORWARDS, MATRIX, VECTOR, FeedForward, TensorSpec
 
 
 @FEED_FORWARDS.register("swiglu")
@@ -57,3 +57,68 @@ class SwiGLU(FeedForward):
         gemm.gated_linear(x, self.gate_up, act, batch.workspace, batch.fault, defer=batch.defer_products)
         out = batch.workspace.get("ffn_out", rows, self.hidden, x.dtype)
         return gemm.linear(act, self.down, out, batch.fault, then_norm=then_norm, defer=batch.defer_products)
+
+
+    def uses_libraries(self) -> set[str]:
+        return {"gemm"} if self.dtype == torch.bfloat16 else set()
+
+
+# activation name -> (number of learned scalars, kernel over [T, I] rows)
+ACTIVATIONS = {"xielu": (2, kernels.xielu)}
+
+
+@FEED_FORWARDS.register("dense")
+class DenseFeedForward(FeedForward):
+    """``down(act(up(x)))`` without gate and biases; the activation may have learned scalars of its own.
+
+    ``xielu``: with the two scalars ``p, q`` of the activation's tensor, ``z > 0: softplus(p) z^2 + z / 2`` and
+    ``z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2`` (float32 arithmetic on the product's result).
+    """
+
+    def __init__(self, *, hidden_size: int, intermediate_size: int, activation: str, dtype, device,
+                 up_name: str = "up", down_name: str = "down", act_name: str = "act") -> None:
+        super().__init__(dtype=dtype, device=device)
+        if activation not in ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r}; known: {sorted(ACTIVATIONS)}")
+        self.hidden, self.inter, self.activation = int(hidden_size), int(intermediate_size), activation
+        self.names = (up_name, down_name, act_name)
+        self.up = self.new_storage((self.inter, self.hidden), MATRIX)
+        self.down = self.new_storage((self.hidden, self.inter), MATRIX)
+        self.scalars = self.new_storage((ACTIVATIONS[activation][0],), VECTOR)
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        up, down, act = self.names
+        return {
+            up: TensorSpec((self.inter, self.hidden)),
+            down: TensorSpec((self.hidden, self.inter)),
+            act: TensorSpec(tuple(self.scalars.shape), VECTOR),
+        }
+
+    def load_tensor(self, name: str, tensor: torch.Tensor) -> None:
+        up, down, act = self.names
+        if name == up:
+            self.up.copy_(tensor)
+        elif name == down:
+            self.down.copy_(tensor)
+        elif name == act:
+            self.scalars.copy_(tensor.to(torch.float32))
+        else:
+            raise KeyError(name)
+
+    def parameter_bytes(self) -> int:
+        return (self.up.numel() + self.down.numel()) * self.up.element_size() + self.scalars.numel() * 4
+
+    def workspace_elements_per_token(self) -> int:
+        return 2 * self.inter + self.hidden
+
+    def uses_libraries(self) -> set[str]:
+        return {"recurrent"} | ({"gemm"} if self.dtype == torch.bfloat16 else set())
+
+    def forward(self, x, batch):
+        rows = x.shape[0]
+        wide = batch.workspace.get("ffn_up", rows, self.inter, x.dtype)
+        gemm.linear(x, self.up, wide, batch.fault)
+        act = batch.workspace.get("ffn_act", rows, self.inter, x.dtype)
+        ACTIVATIONS[self.activation][1](wide, act, self.scalars)
+        out = batch.workspace.get("ffn_out", rows, self.hidden, x.dtype)
+        return gemm.linear(act, self.down, out, batch.fault)

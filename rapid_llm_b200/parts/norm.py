@@ -20,17 +20,18 @@ FIRST, ADD, PLAIN = 0, 1, 2
 class RMSNorm(Norm):
     reads_deferred = True       # it launches through ops.kernels, which runs queued products first
 
-    def __init__(self, *, size: int, eps: float, dtype, device) -> None:
+    def __init__(self, *, size: int, eps: float, dtype, device, name: str = "weight") -> None:
         super().__init__(dtype=dtype, device=device)
         self.size = int(size)
         self.eps = float(eps)
+        self.name = name          # the tensor's name after the part's prefix (may be empty)
         self.weight = self.new_storage((self.size,), VECTOR)
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
-        return {"weight": TensorSpec((self.size,), VECTOR, init="ones_normal")}
+        return {self.name: TensorSpec((self.size,), VECTOR, init="ones_normal")}
 
     def load_tensor(self, name: str, tensor: torch.Tensor) -> None:
-        if name != "weight":
+        if name != self.name:
             raise KeyError(name)
         self.weight.copy_(tensor.to(torch.float32))
 
@@ -46,15 +47,18 @@ class RMSNorm(Norm):
             return None
         return gemm.FollowingNorm(residual, self.weight, self.eps, batch.workspace)
 
-    def forward(self, x, residual, batch, *, mode, write_residual, row_index=None, name="normed"):
+    def forward(self, x, residual, batch, *, mode, write_residual, row_index=None, name="normed", addend=None):
         """Norm of ``x`` (``FIRST``/``PLAIN``) or of ``x + residual`` (``ADD``).
 
         With ``write_residual`` the float32 sum is stored into ``residual``.  ``row_index``
-        selects input rows (the rows whose logits are wanted, for the final norm).
+        selects input rows (the rows whose logits are wanted, for the final norm).  ``addend``
+        (:class:`~rapid_llm_b200.parts.base.StreamAddend`) is added to the sum before it is stored.
         """
         rows = x.shape[0] if row_index is None else row_index.numel()
         out = batch.workspace.get(name, rows, self.size, x.dtype, min_rows=None if row_index is None else 64)
         return kernels.add_rmsnorm(
             x, residual, self.weight, out, self.eps,
             mode=mode, write_residual=write_residual, row_index=row_index,
+            extra_rows=None if addend is None else addend.rows,
+            extra_vector=None if addend is None else addend.vector,
         )

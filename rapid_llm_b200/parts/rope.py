@@ -40,3 +40,18 @@ class RotaryEmbedding(PositionEncoding):
 
     def tables(self) -> tuple[torch.Tensor, torch.Tensor]:
         return self.cos, self.sin
+
+
+@POSITION_ENCODINGS.register("none")
+class NoPositions(PositionEncoding):
+    """No rotation: positions do not enter the scores.  The tables have no columns, and as many rows as
+    positions are allowed (the rotation kernel checks a position against the rows)."""
+
+    def __init__(self, *, max_positions: int, dtype, device) -> None:
+        super().__init__(dtype=dtype, device=device)
+        self.head_dim, self.rotary_dim, self.max_positions = 0, 0, int(max_positions)
+        self.cos = torch.empty((self.max_positions, 0), dtype=torch.float32, device=self.device)
+        self.sin = self.cos
+
+    def tables(self) -> tuple[torch.Tensor, torch.Tensor]:
+        return self.cos, self.sin
