@@ -589,7 +589,8 @@ def main() -> int:
                         "benchmark's; 14b and 32b are the other shapes of the same architecture")
     parser.add_argument("--context", type=int, default=CONTEXT, help="longest sequence the engine is set up for")
     parser.add_argument("--points", default="1,64", help="other batch sizes decoded beside --batch")
-    parser.add_argument("--workload", choices=["decode", "serve"], default="decode", help="decode: the benchmark "
+    parser.add_argument("--sizes", default="2048,4096", help="widths of the models of --workload kopatar")
+    parser.add_argument("--workload", choices=["decode", "serve", "kopatar"], default="decode", help="decode: the benchmark "
                         "(timed decode steps, a prefill, the points); serve: continuous batching of --requests "
                         "prompts of mixed lengths through generate()")
     parser.add_argument("--requests", type=int, default=64, help="requests of the serve workload")
@@ -617,6 +618,15 @@ def main() -> int:
     globals()["TEMPERATURE"] = args.temperature
     globals()["PROMPT_LEN"] = args.prompt_len
     globals()["CONTEXT"] = args.context
+    if args.workload == "kopatar":
+        # the recurrent architecture beside Qwen3 at equal sizes, and its kernels alone (not the benchmark's workload)
+        from rapid_llm_b200.ops.recurrent_compare import run as kopatar_run
+
+        with ClockSampler() as clocks:
+            result = kopatar_run([int(size) for size in args.sizes.split(",") if size], measured_peaks()["hbm_gbs"])
+        result["clocks"] = clocks.summary()
+        print(json.dumps(result))
+        return 0
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))
     return 0

@@ -192,8 +192,10 @@ __global__ void rotate_heads_kernel(const T* __restrict__ in, int in_stride, int
 //
 // A block owns (entry, head, a tile of columns of S) and walks the entry's tokens in order.  A column
 // is shared by `partners` lanes of one warp, each holding kRows consecutive rows of it in registers;
-// sums over rows end in a fixed tree of shuffles.  q, k, row decays, v and the per-token numbers of a
-// run of tokens are staged in shared memory by the whole block, so the walk itself waits on nothing.
+// sums over rows end in a fixed tree of shuffles, so a token's result depends on nothing but the
+// tokens before it.  q, k, row decays, v and the per-token numbers of a run of tokens are brought into
+// shared memory by asynchronous copies while the run before is walked.  In the slot's row a head's
+// state lies column by column (S^T, [vdim][dim]), so that a lane's rows are consecutive floats.
 struct ScanArgs {
   const float* q; int q_stride;
   const float* k; int k_stride;
@@ -207,85 +209,182 @@ struct ScanArgs {
   const int* cu_seqlens; const int* entry_slot; const int* entry_start;
   int heads, kv_heads, dim, vdim, slots;
   int partners, run;
+  int wide_in;      // q, k, v (and row decays) can be fetched 16 bytes at a time
   int* fault;
 };
 
-constexpr int kScanThreads = 128;
+constexpr int kScanThreads = 256;
 
-template <int kRows>
+__device__ __forceinline__ void copy_async4(float* shared, const float* global) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<unsigned>(__cvta_generic_to_shared(shared))),
+               "l"(global) : "memory");
+}
+__device__ __forceinline__ void copy_async16(float* shared, const float* global) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<unsigned>(__cvta_generic_to_shared(shared))),
+               "l"(global) : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory"); }
+
+template <int kRows, int kPartners>
 __global__ void __launch_bounds__(kScanThreads) linear_scan_kernel(const ScanArgs a) {
-  extern __shared__ float staged[];
-  pdl_trigger();
+  extern __shared__ __align__(16) float staged[];
+  // Its successor is let in only when the walk is over (below): a kernel that waits at its start still holds
+  // warp slots, and the walk is bound by its own latencies, which more resident warps do not shorten.
   const int e = blockIdx.x, head = blockIdx.y;
-  const int partners = a.partners, cols_per_warp = 32 / partners;
+  constexpr int partners = kPartners, cols_per_warp = 32 / kPartners;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int part = lane / cols_per_warp, col_in_warp = lane - part * cols_per_warp;
-  const int tile_cols = (kScanThreads / 32) * cols_per_warp;
+  constexpr int tile_cols = (kScanThreads / 32) * cols_per_warp;
   const int col_in_tile = warp * cols_per_warp + col_in_warp;
   const int col = blockIdx.z * tile_cols + col_in_tile;
   const bool col_ok = col < a.vdim;
   const int row0 = part * kRows;
-  const int dim_padded = partners * kRows;
+  constexpr int dim_padded = partners * kRows;
   const int kv_head = head / (a.heads / a.kv_heads);
 
   const int first = a.cu_seqlens[e], length = a.cu_seqlens[e + 1] - first, start = a.entry_start[e];
   int slot = a.entry_slot[e];
-  bool slot_ok = slot >= 0 && slot < a.slots;
+  const bool slot_ok = slot >= 0 && slot < a.slots;
   if (!slot_ok) {
     if (threadIdx.x == 0) atomicOr(a.fault, kFaultSlot);
     slot = 0;
   }
-  float* home = a.state + slot * a.state_stride + a.state_off + static_cast<size_t>(head) * a.dim * a.vdim;
+  float* home = a.state + slot * a.state_stride + a.state_off + static_cast<size_t>(head) * a.dim * a.vdim +
+                static_cast<size_t>(col_ok ? col : 0) * a.dim + row0;
+  const bool wide = (a.dim & 3) == 0 && (reinterpret_cast<uintptr_t>(home) & 15) == 0;   // kRows is a multiple of 4
 
-  // shared: k, q (and row decays) [run][dim_padded]; v [run][tile_cols]; beta / v_scale / decay [run] each
+  // two buffers, each: k, q (and row decays) [run][dim_padded]; v [run][tile_cols]; write strength, decay [run]
   const int run = a.run;
-  float* sk = staged;
-  float* sq = sk + run * dim_padded;
-  float* sg = sq + run * dim_padded;
-  float* sv = sg + (a.decay_mode == 2 ? run * dim_padded : 0);
-  float* sbeta = sv + run * tile_cols;
-  float* sdecay = sbeta + run;
-
-  pdl_wait();
-  float S[kRows];
-#pragma unroll
-  for (int r = 0; r < kRows; ++r) {
-    const int i = row0 + r;
-    S[r] = (start > 0 && col_ok && i < a.dim) ? home[static_cast<size_t>(i) * a.vdim + col] : 0.0f;
-  }
+  const int per_token = (a.decay_mode == 2 ? 3 : 2) * dim_padded + tile_cols + 2;
+  const int buffer_floats = (run * per_token + 3) & ~3;      // both buffers start on 16 bytes
   const float fixed_decay = a.decay_mode == 0 ? a.decay[head] : 1.0f;
   const float skip = a.skip ? a.skip[head] : 0.0f;
+  const float* strength = a.beta ? a.beta : a.v_scale;
 
-  for (int base = 0; base < length; base += run) {
+  auto stage = [&](int base, float* buffer) {
     const int count = min(run, length - base);
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < count * dim_padded; idx += kScanThreads) {
-      const int tt = idx / dim_padded, i = idx - tt * dim_padded;
-      const size_t t = static_cast<size_t>(first + base + tt);
-      const bool in = i < a.dim;
-      sk[idx] = in ? a.k[t * a.k_stride + kv_head * a.dim + i] : 0.0f;
-      sq[idx] = in ? a.q[t * a.q_stride + kv_head * a.dim + i] : 0.0f;
-      if (a.decay_mode == 2) sg[idx] = in ? a.decay[(t * a.heads + head) * a.dim + i] : 1.0f;
-    }
-    for (int idx = threadIdx.x; idx < count * tile_cols; idx += kScanThreads) {
-      const int tt = idx / tile_cols, j = idx - tt * tile_cols;
-      const int c = blockIdx.z * tile_cols + j;
-      sv[idx] = c < a.vdim ? a.v[static_cast<size_t>(first + base + tt) * a.v_stride + head * a.vdim + c] : 0.0f;
+    float* sk = buffer;
+    float* sq = sk + run * dim_padded;
+    float* sg = sq + run * dim_padded;
+    float* sv = sg + (a.decay_mode == 2 ? run * dim_padded : 0);
+    float* sbeta = sv + run * tile_cols;
+    float* sdecay = sbeta + run;
+    if (a.wide_in) {
+      const int quads = dim_padded >> 2, tile_quads = tile_cols >> 2;
+      for (int idx = threadIdx.x; idx < count * quads; idx += kScanThreads) {
+        const int tt = idx / quads, i = (idx - tt * quads) << 2;
+        const size_t t = static_cast<size_t>(first + base + tt);
+        const int at = tt * dim_padded + i;
+        if (i < a.dim) {
+          copy_async16(sk + at, a.k + t * a.k_stride + kv_head * a.dim + i);
+          copy_async16(sq + at, a.q + t * a.q_stride + kv_head * a.dim + i);
+          if (a.decay_mode == 2) copy_async16(sg + at, a.decay + (t * a.heads + head) * a.dim + i);
+        } else {
+          *reinterpret_cast<float4*>(sk + at) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          *reinterpret_cast<float4*>(sq + at) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          if (a.decay_mode == 2) *reinterpret_cast<float4*>(sg + at) = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+        }
+      }
+      for (int idx = threadIdx.x; idx < count * tile_quads; idx += kScanThreads) {
+        const int tt = idx / tile_quads, j = (idx - tt * tile_quads) << 2;
+        const int c = blockIdx.z * tile_cols + j;
+        float* to = sv + tt * tile_cols + j;
+        if (c < a.vdim) copy_async16(to, a.v + static_cast<size_t>(first + base + tt) * a.v_stride + head * a.vdim + c);
+        else *reinterpret_cast<float4*>(to) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < count * dim_padded; idx += kScanThreads) {
+        const int tt = idx / dim_padded, i = idx - tt * dim_padded;
+        const size_t t = static_cast<size_t>(first + base + tt);
+        if (i < a.dim) {
+          copy_async4(sk + idx, a.k + t * a.k_stride + kv_head * a.dim + i);
+          copy_async4(sq + idx, a.q + t * a.q_stride + kv_head * a.dim + i);
+          if (a.decay_mode == 2) copy_async4(sg + idx, a.decay + (t * a.heads + head) * a.dim + i);
+        } else {
+          sk[idx] = 0.0f;
+          sq[idx] = 0.0f;
+          if (a.decay_mode == 2) sg[idx] = 1.0f;
+        }
+      }
+      for (int idx = threadIdx.x; idx < count * tile_cols; idx += kScanThreads) {
+        const int tt = idx / tile_cols, j = idx - tt * tile_cols;
+        const int c = blockIdx.z * tile_cols + j;
+        if (c < a.vdim) copy_async4(sv + idx, a.v + static_cast<size_t>(first + base + tt) * a.v_stride + head * a.vdim + c);
+        else sv[idx] = 0.0f;
+      }
     }
     for (int tt = threadIdx.x; tt < count; tt += kScanThreads) {
       const size_t at = static_cast<size_t>(first + base + tt) * a.heads + head;
-      sbeta[tt] = a.beta ? a.beta[at] : (a.v_scale ? a.v_scale[at] : 1.0f);
-      sdecay[tt] = a.decay_mode == 1 ? a.decay[at] : fixed_decay;
+      if (strength) copy_async4(sbeta + tt, strength + at); else sbeta[tt] = 1.0f;
+      if (a.decay_mode == 1) copy_async4(sdecay + tt, a.decay + at); else sdecay[tt] = fixed_decay;
+    }
+    copy_async_commit();
+  };
+
+  pdl_wait();
+  if (length > 0) stage(0, staged);
+  float S[kRows];
+#pragma unroll
+  for (int r = 0; r < kRows; ++r) S[r] = 0.0f;
+  if (start > 0 && col_ok) {
+    if (wide) {
+#pragma unroll
+      for (int r = 0; r < kRows; r += 4) {
+        if (row0 + r < a.dim) {
+          const float4 four = *reinterpret_cast<const float4*>(home + r);
+          S[r] = four.x; S[r + 1] = four.y; S[r + 2] = four.z; S[r + 3] = four.w;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < kRows; ++r)
+        if (row0 + r < a.dim) S[r] = home[r];
+    }
+  }
+
+  int flip = 0;
+  for (int base = 0; base < length; base += run, flip ^= 1) {
+    const int count = min(run, length - base);
+    float* buffer = staged + flip * buffer_floats;
+    if (base + run < length) {
+      stage(base + run, staged + (flip ^ 1) * buffer_floats);   // the next run, while this one is walked
+      copy_async_wait<1>();
+    } else {
+      copy_async_wait<0>();
     }
     __syncthreads();
-    for (int tt = 0; tt < count; ++tt) {
-      const float* kk = sk + tt * dim_padded + row0;
-      const float* qq = sq + tt * dim_padded + row0;
-      const float vj = sv[tt * tile_cols + col_in_tile];
-      if (a.decay_mode == 2) {
-        const float* gg = sg + tt * dim_padded + row0;
+    const float* sk = buffer;
+    const float* sq = sk + run * dim_padded;
+    const float* sg = sq + run * dim_padded;
+    const float* sv = sg + (a.decay_mode == 2 ? run * dim_padded : 0);
+    const float* sbeta = sv + run * tile_cols;
+    const float* sdecay = sbeta + run;
+    // a lane's rows are 16-byte aligned runs of shared memory: fetched four at a time, no two lanes of a
+    // quarter-warp meet in a bank; every pointer of the walk moves by a constant per token
+    const float* kp = sk + row0;
+    const float* qp = sq + row0;
+    const float* gp = sg + row0;
+    const float* vp = sv + col_in_tile;
+    float* op = a.out + static_cast<size_t>(first + base) * a.out_stride + head * a.vdim + (col_ok ? col : 0);
+    const bool writes = part == 0 && col_ok;
+    for (int tt = 0; tt < count; ++tt, kp += dim_padded, qp += dim_padded, gp += dim_padded, vp += tile_cols, op += a.out_stride) {
+      float kk[kRows], qq[kRows];
 #pragma unroll
-        for (int r = 0; r < kRows; ++r) S[r] *= gg[r];
+      for (int r = 0; r < kRows; r += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kp + r);
+        const float4 q4 = *reinterpret_cast<const float4*>(qp + r);
+        kk[r] = k4.x; kk[r + 1] = k4.y; kk[r + 2] = k4.z; kk[r + 3] = k4.w;
+        qq[r] = q4.x; qq[r + 1] = q4.y; qq[r + 2] = q4.z; qq[r + 3] = q4.w;
+      }
+      const float vj = *vp;
+      if (a.decay_mode == 2) {
+#pragma unroll
+        for (int r = 0; r < kRows; r += 4) {
+          const float4 g4 = *reinterpret_cast<const float4*>(gp + r);
+          S[r] *= g4.x; S[r + 1] *= g4.y; S[r + 2] *= g4.z; S[r + 3] *= g4.w;
+        }
       } else {
         const float d = sdecay[tt];
 #pragma unroll
@@ -296,6 +395,7 @@ __global__ void __launch_bounds__(kScanThreads) linear_scan_kernel(const ScanArg
         float seen = 0.0f;
 #pragma unroll
         for (int r = 0; r < kRows; ++r) seen += S[r] * kk[r];
+#pragma unroll
         for (int offset = cols_per_warp; offset < 32; offset <<= 1) seen += __shfl_xor_sync(0xffffffffu, seen, offset);
         u = sbeta[tt] * (vj - seen);
       } else {
@@ -307,16 +407,22 @@ __global__ void __launch_bounds__(kScanThreads) linear_scan_kernel(const ScanArg
         S[r] += kk[r] * u;
         o += S[r] * qq[r];
       }
-      for (int offset = cols_per_warp; offset < 32; offset <<= 1) o += __shfl_xor_sync(0xffffffffu, o, offset);
-      if (part == 0 && col_ok)
-        a.out[static_cast<size_t>(first + base + tt) * a.out_stride + head * a.vdim + col] = o + skip * vj;
-    }
-  }
-  if (slot_ok && col_ok) {
 #pragma unroll
-    for (int r = 0; r < kRows; ++r) {
-      const int i = row0 + r;
-      if (i < a.dim) home[static_cast<size_t>(i) * a.vdim + col] = S[r];
+      for (int offset = cols_per_warp; offset < 32; offset <<= 1) o += __shfl_xor_sync(0xffffffffu, o, offset);
+      if (writes) *op = o + skip * vj;
+    }
+    __syncthreads();     // the buffer is free for the run after the next
+  }
+  pdl_trigger();
+  if (slot_ok && col_ok) {
+    if (wide) {
+#pragma unroll
+      for (int r = 0; r < kRows; r += 4)
+        if (row0 + r < a.dim) *reinterpret_cast<float4*>(home + r) = make_float4(S[r], S[r + 1], S[r + 2], S[r + 3]);
+    } else {
+#pragma unroll
+      for (int r = 0; r < kRows; ++r)
+        if (row0 + r < a.dim) home[r] = S[r];
     }
   }
 }
@@ -469,9 +575,8 @@ int rl_linear_scan(const float* q, int q_stride, const float* k, int k_stride, c
   if (heads < 1 || kv_heads < 1 || heads % kv_heads || dim < 1 || dim > 1024 || vdim < 1 || decay_mode < 0 ||
       decay_mode > 2 || decay == nullptr)
     return static_cast<int>(cudaErrorInvalidValue);
-  // rows a lane holds: a quarter of the column where that is at most 32, and then as many lanes a column as it takes
-  int rows = 4;
-  while (rows < 32 && rows * 4 < dim) rows *= 2;
+  // rows a lane holds: few, so that a column's work spreads over many lanes; as many lanes a column as it takes
+  const int rows = dim <= 32 ? 4 : (dim <= 256 ? 8 : (dim <= 512 ? 16 : 32));
   int partners = 1;
   while (partners * rows < dim) partners *= 2;
   rl::ScanArgs a;
@@ -481,17 +586,23 @@ int rl_linear_scan(const float* q, int q_stride, const float* k, int k_stride, c
   a.cu_seqlens = cu_seqlens; a.entry_slot = entry_slot; a.entry_start = entry_start;
   a.heads = heads; a.kv_heads = kv_heads; a.dim = dim; a.vdim = vdim; a.slots = slots; a.partners = partners;
   a.fault = fault;
+  auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  a.wide_in = dim % 4 == 0 && vdim % 4 == 0 && q_stride % 4 == 0 && k_stride % 4 == 0 && v_stride % 4 == 0 &&
+              aligned(q) && aligned(k) && aligned(v) && (decay_mode != 2 || aligned(decay));
   const int tile_cols = (rl::kScanThreads / 32) * (32 / partners);
   const int dim_padded = partners * rows;
   const int per_token = (decay_mode == 2 ? 3 : 2) * dim_padded + tile_cols + 2;
-  int run = (40 * 1024 / 4) / per_token;
+  int run = (20 * 1024 / 4) / per_token;      // two buffers of a run each within 40 KB
   a.run = run > 16 ? 16 : (run < 1 ? 1 : run);
-  const size_t smem = static_cast<size_t>(a.run) * per_token * sizeof(float);
+  const size_t smem = 2 * static_cast<size_t>((a.run * per_token + 3) & ~3) * sizeof(float);
   const dim3 grid(entries, heads, (vdim + tile_cols - 1) / tile_cols), block(rl::kScanThreads);
-  if (rows == 4) return rl::launch_kernel(rl::linear_scan_kernel<4>, grid, block, smem, stream, pdl != 0, a);
-  if (rows == 8) return rl::launch_kernel(rl::linear_scan_kernel<8>, grid, block, smem, stream, pdl != 0, a);
-  if (rows == 16) return rl::launch_kernel(rl::linear_scan_kernel<16>, grid, block, smem, stream, pdl != 0, a);
-  return rl::launch_kernel(rl::linear_scan_kernel<32>, grid, block, smem, stream, pdl != 0, a);
+#define RL_SCAN(R, P) \
+  if (rows == R && partners == P) return rl::launch_kernel(rl::linear_scan_kernel<R, P>, grid, block, smem, stream, pdl != 0, a)
+  RL_SCAN(4, 1); RL_SCAN(4, 2); RL_SCAN(4, 4); RL_SCAN(4, 8);
+  RL_SCAN(8, 8); RL_SCAN(8, 16); RL_SCAN(8, 32);
+  RL_SCAN(16, 32); RL_SCAN(32, 32);
+#undef RL_SCAN
+  return static_cast<int>(cudaErrorInvalidValue);
 }
 
 // y_f32: y is float32 whatever the engine's dtype (the result of a recurrence); else y has the engine's dtype.

@@ -219,7 +219,7 @@ class GQAAttention(Mixer):
             clusters = kernels.attention_decode_clusters(self.d, device) or None
         self._items = AttentionItems(self.hq // self.hkv, self.hkv, self.d, sms, clusters)
         self.position = POSITION_ENCODINGS.build(position, dtype=dtype, device=device)
-        self.rotary_dim = int(getattr(self.position, "rotary_dim", self.d))
+        self.rotary_dim = int(position.params.get("rotary_dim", getattr(self.position, "rotary_dim", self.d)))
 
         kv_rows = 0 if self.shares_cache else 2 * self.hkv * self.d
         self.qkv = self.new_storage((self.hq * self.d + kv_rows, self.hidden), MATRIX)
