@@ -9,6 +9,8 @@
 // recurrence consumes (decays, step sizes, gates, unit vectors, the state) is float32 in both engine
 // precisions; the recurrence runs token by token in a fixed order, so a row's result does not depend
 // on how the tokens were cut into steps or on what else is in the batch.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace rl {
@@ -369,48 +371,75 @@ __global__ void __launch_bounds__(kScanThreads) linear_scan_kernel(const ScanArg
     const float* vp = sv + col_in_tile;
     float* op = a.out + static_cast<size_t>(first + base) * a.out_stride + head * a.vdim + (col_ok ? col : 0);
     const bool writes = part == 0 && col_ok;
-    for (int tt = 0; tt < count; ++tt, kp += dim_padded, qp += dim_padded, gp += dim_padded, vp += tile_cols, op += a.out_stride) {
-      float kk[kRows], qq[kRows];
+    // Tokens are walked in groups of four: the state passes from one to the next, but their read-outs' sums over
+    // lanes are independent and run side by side after the group, one shuffle's wait for four.  A token's own
+    // arithmetic is the same whatever group it falls into.
+    auto walk = [&](auto group_size, int tt) {
+      constexpr int kGroup = decltype(group_size)::value;
+      float o[kGroup], vv[kGroup];
 #pragma unroll
-      for (int r = 0; r < kRows; r += 4) {
-        const float4 k4 = *reinterpret_cast<const float4*>(kp + r);
-        const float4 q4 = *reinterpret_cast<const float4*>(qp + r);
-        kk[r] = k4.x; kk[r + 1] = k4.y; kk[r + 2] = k4.z; kk[r + 3] = k4.w;
-        qq[r] = q4.x; qq[r + 1] = q4.y; qq[r + 2] = q4.z; qq[r + 3] = q4.w;
-      }
-      const float vj = *vp;
-      if (a.decay_mode == 2) {
+      for (int g = 0; g < kGroup; ++g) {
+        float kk[kRows], qq[kRows];
 #pragma unroll
         for (int r = 0; r < kRows; r += 4) {
-          const float4 g4 = *reinterpret_cast<const float4*>(gp + r);
-          S[r] *= g4.x; S[r + 1] *= g4.y; S[r + 2] *= g4.z; S[r + 3] *= g4.w;
+          const float4 k4 = *reinterpret_cast<const float4*>(kp + g * dim_padded + r);
+          const float4 q4 = *reinterpret_cast<const float4*>(qp + g * dim_padded + r);
+          kk[r] = k4.x; kk[r + 1] = k4.y; kk[r + 2] = k4.z; kk[r + 3] = k4.w;
+          qq[r] = q4.x; qq[r + 1] = q4.y; qq[r + 2] = q4.z; qq[r + 3] = q4.w;
         }
-      } else {
-        const float d = sdecay[tt];
+        const float vj = vp[g * tile_cols];
+        if (a.decay_mode == 2) {
 #pragma unroll
-        for (int r = 0; r < kRows; ++r) S[r] *= d;
+          for (int r = 0; r < kRows; r += 4) {
+            const float4 g4 = *reinterpret_cast<const float4*>(gp + g * dim_padded + r);
+            S[r] *= g4.x; S[r + 1] *= g4.y; S[r + 2] *= g4.z; S[r + 3] *= g4.w;
+          }
+        } else {
+          const float d = sdecay[tt + g];
+#pragma unroll
+          for (int r = 0; r < kRows; ++r) S[r] *= d;
+        }
+        float u;
+        if (a.beta) {
+          float seen = 0.0f, seen_odd = 0.0f;
+#pragma unroll
+          for (int r = 0; r < kRows; r += 2) {
+            seen += S[r] * kk[r];
+            seen_odd += S[r + 1] * kk[r + 1];
+          }
+          seen += seen_odd;
+#pragma unroll
+          for (int offset = cols_per_warp; offset < 32; offset <<= 1) seen += __shfl_xor_sync(0xffffffffu, seen, offset);
+          u = sbeta[tt + g] * (vj - seen);
+        } else {
+          u = sbeta[tt + g] * vj;
+        }
+        float even = 0.0f, odd = 0.0f;
+#pragma unroll
+        for (int r = 0; r < kRows; r += 2) {
+          S[r] += kk[r] * u;
+          S[r + 1] += kk[r + 1] * u;
+          even += S[r] * qq[r];
+          odd += S[r + 1] * qq[r + 1];
+        }
+        o[g] = even + odd;
+        vv[g] = vj;
       }
-      float u;
-      if (a.beta) {
-        float seen = 0.0f;
 #pragma unroll
-        for (int r = 0; r < kRows; ++r) seen += S[r] * kk[r];
+      for (int offset = cols_per_warp; offset < 32; offset <<= 1) {
 #pragma unroll
-        for (int offset = cols_per_warp; offset < 32; offset <<= 1) seen += __shfl_xor_sync(0xffffffffu, seen, offset);
-        u = sbeta[tt] * (vj - seen);
-      } else {
-        u = sbeta[tt] * vj;
+        for (int g = 0; g < kGroup; ++g) o[g] += __shfl_xor_sync(0xffffffffu, o[g], offset);
       }
-      float o = 0.0f;
+      if (writes) {
 #pragma unroll
-      for (int r = 0; r < kRows; ++r) {
-        S[r] += kk[r] * u;
-        o += S[r] * qq[r];
+        for (int g = 0; g < kGroup; ++g) op[static_cast<size_t>(g) * a.out_stride] = o[g] + skip * vv[g];
       }
-#pragma unroll
-      for (int offset = cols_per_warp; offset < 32; offset <<= 1) o += __shfl_xor_sync(0xffffffffu, o, offset);
-      if (writes) *op = o + skip * vj;
-    }
+      kp += kGroup * dim_padded; qp += kGroup * dim_padded; gp += kGroup * dim_padded; vp += kGroup * tile_cols;
+      op += static_cast<size_t>(kGroup) * a.out_stride;
+    };
+    int tt = 0;
+    for (; tt + 4 <= count; tt += 4) walk(std::integral_constant<int, 4>{}, tt);
+    for (; tt < count; ++tt) walk(std::integral_constant<int, 1>{}, tt);
     __syncthreads();     // the buffer is free for the run after the next
   }
   pdl_trigger();
