@@ -36,39 +36,108 @@ constexpr int kMaxTaps = 16;
 // those of this step from the rows of x, the K - 1 before them from the slot's tail (float32,
 // [K - 1, C], oldest first), zeros before position 0.  x is columns col0 .. col0 + C - 1 of rows of
 // length x_stride.
+constexpr int kConvRows = 8;
+
 template <typename T>
+__device__ __forceinline__ float2 load_pair(const T* p);
+template <>
+__device__ __forceinline__ float2 load_pair<float>(const float* p) { return *reinterpret_cast<const float2*>(p); }
+template <>
+__device__ __forceinline__ float2 load_pair<__nv_bfloat16>(const __nv_bfloat16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+
+// A thread owns kLanes (1 or 2) neighbouring channels over kConvRows consecutive packed rows and slides the taps'
+// window down them, so a row of x is fetched once, not once per tap.  kLanes == 2 wants even C, col0 and x_stride.
+// kTaps > 0: the taps' number is known when compiling and the window lives in registers; 0: any number up to kMaxTaps.
+template <typename T, int kLanes, int kTaps>
 __global__ void causal_conv_silu_kernel(const T* __restrict__ x, int x_stride, int col0,
                                         const float* __restrict__ taps, const float* __restrict__ bias,
                                         const float* __restrict__ state, long long state_stride, int state_off,
                                         float* __restrict__ out, const int* __restrict__ cu_seqlens,
                                         const int* __restrict__ entry_slot, const int* __restrict__ entry_start,
-                                        int entries, int tokens, int C, int K, int slots, int* __restrict__ fault) {
+                                        int entries, int tokens, int C, int taps_given, int slots, int* __restrict__ fault) {
   pdl_trigger();
+  const int K = kTaps > 0 ? kTaps : taps_given;
+  constexpr int kHeld = kTaps > 0 ? kTaps : kMaxTaps;
+  const int groups = C / kLanes, tiles = (tokens + kConvRows - 1) / kConvRows;
+  const long long total = static_cast<long long>(tiles) * groups;
+  const long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (idx >= total) {
+    pdl_wait();
+    return;
+  }
+  const int tile = static_cast<int>(idx / groups), c = static_cast<int>(idx - static_cast<long long>(tile) * groups) * kLanes;
+  float w[kLanes][kHeld], b[kLanes];
+#pragma unroll
+  for (int l = 0; l < kLanes; ++l) {
+    b[l] = bias ? bias[c + l] : 0.0f;
+#pragma unroll
+    for (int d = 0; d < kHeld; ++d)
+      if (d < K) w[l][d] = taps[static_cast<size_t>(c + l) * K + d];     // w[K - 1] is the current token's
+  }
+  const int t0 = tile * kConvRows;
+  int e = entry_of(cu_seqlens, entries, t0);
   pdl_wait();
-  const long long total = static_cast<long long>(tokens) * C;
-  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
-       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int t = static_cast<int>(idx / C), c = static_cast<int>(idx - static_cast<long long>(t) * C);
-    const int e = entry_of(cu_seqlens, entries, t);
+  // the window: hist[d] is the input d rows back (hist[0] the current row's)
+  float hist[kLanes][kHeld];
+  int filled_for = -1;      // the entry the window was filled for
+  for (int t = t0; t < min(t0 + kConvRows, tokens); ++t) {
+    while (t >= cu_seqlens[e + 1]) ++e;
     const int local = t - cu_seqlens[e], start = entry_start[e];
-    int slot = entry_slot[e];
-    if (slot < 0 || slot >= slots) {
-      atomicOr(fault, kFaultSlot);
-      slot = 0;
-    }
-    const float* tail = state + slot * state_stride + state_off;
-    float acc = bias ? bias[c] : 0.0f;
-    for (int d = 0; d < K; ++d) {
-      const int at = local - d;
-      float v = 0.0f;
-      if (at >= 0) {
-        v = to_float(x[static_cast<size_t>(t - d) * x_stride + col0 + c]);
-      } else if (start + at >= 0) {
-        v = tail[static_cast<size_t>(K - 1 + at) * C + c];
+    if (filled_for != e) {      // first row of this tile that belongs to entry e: fetch the K - 1 inputs before it
+      int slot = entry_slot[e];
+      if (slot < 0 || slot >= slots) {
+        atomicOr(fault, kFaultSlot);
+        slot = 0;
       }
-      acc += taps[static_cast<size_t>(c) * K + (K - 1 - d)] * v;
+      const float* tail = state + slot * state_stride + state_off;
+#pragma unroll
+      for (int d = 1; d < kHeld; ++d) {
+        if (d >= K) break;
+        const int at = local - d;
+#pragma unroll
+        for (int l = 0; l < kLanes; ++l) hist[l][d] = 0.0f;
+        if (at >= 0) {
+          if constexpr (kLanes == 2) {
+            const float2 v = load_pair(x + static_cast<size_t>(t - d) * x_stride + col0 + c);
+            hist[0][d] = v.x; hist[1][d] = v.y;
+          } else {
+            hist[0][d] = to_float(x[static_cast<size_t>(t - d) * x_stride + col0 + c]);
+          }
+        } else if (start + at >= 0) {
+#pragma unroll
+          for (int l = 0; l < kLanes; ++l) hist[l][d] = tail[static_cast<size_t>(K - 1 + at) * C + c + l];
+        }
+      }
+      filled_for = e;
     }
-    out[idx] = silu_f(acc);
+    if constexpr (kLanes == 2) {
+      const float2 v = load_pair(x + static_cast<size_t>(t) * x_stride + col0 + c);
+      hist[0][0] = v.x; hist[1][0] = v.y;
+    } else {
+      hist[0][0] = to_float(x[static_cast<size_t>(t) * x_stride + col0 + c]);
+    }
+    float acc[kLanes];
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) {
+      acc[l] = b[l];
+#pragma unroll
+      for (int d = 0; d < kHeld; ++d)
+        if (d < K) acc[l] += w[l][K - 1 - d] * hist[l][d];
+      acc[l] = silu_f(acc[l]);
+    }
+    if constexpr (kLanes == 2) {
+      *reinterpret_cast<float2*>(out + static_cast<size_t>(t) * C + c) = make_float2(acc[0], acc[1]);
+    } else {
+      out[static_cast<size_t>(t) * C + c] = acc[0];
+    }
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) {
+#pragma unroll
+      for (int d = kHeld - 1; d > 0; --d)
+        if (d < K) hist[l][d] = hist[l][d - 1];
+    }
   }
 }
 
@@ -158,14 +227,16 @@ __global__ void rotate_heads_kernel(const T* __restrict__ in, int in_stride, int
                                     float* __restrict__ out, const int* __restrict__ positions,
                                     const float* __restrict__ inv_freq, int heads, int dim, int vdim, int rot,
                                     float k_scale, int tokens) {
+  extern __shared__ float angles[];      // cos, then sin, of the token's rot / 2 angles: the same for every head
   pdl_trigger();
-  pdl_wait();
   const int t = blockIdx.x;
-  if (t >= tokens) return;
-  const T* row = in + static_cast<size_t>(t) * in_stride;
   const int qk = heads * dim, half = rot >> 1;
-  float* o = out + static_cast<size_t>(t) * (2 * qk + heads * vdim);
   const float pos = static_cast<float>(positions[t]);
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * inv_freq[i], &angles[half + i], &angles[i]);
+  pdl_wait();
+  __syncthreads();
+  const T* row = in + static_cast<size_t>(t) * in_stride;
+  float* o = out + static_cast<size_t>(t) * (2 * qk + heads * vdim);
   for (int idx = threadIdx.x; idx < 2 * qk; idx += blockDim.x) {
     const bool is_k = idx >= qk;
     const int within = is_k ? idx - qk : idx;
@@ -174,9 +245,8 @@ __global__ void rotate_heads_kernel(const T* __restrict__ in, int in_stride, int
     float v = to_float(src[i]);
     if (i < rot) {
       const int pair = i < half ? i : i - half;
-      float s, c;
-      sincosf(pos * inv_freq[pair], &s, &c);
-      v = i < half ? v * c - to_float(src[i + half]) * s : v * c + to_float(src[i - half]) * s;
+      const float c = angles[pair], sn = angles[half + pair];
+      v = i < half ? v * c - to_float(src[i + half]) * sn : v * c + to_float(src[i - half]) * sn;
     }
     o[idx] = is_k ? v * k_scale : v;
   }
@@ -499,19 +569,123 @@ __global__ void gated_norm_kernel(const TY* __restrict__ y, int y_stride, const 
   }
 }
 
+// The same with one warp per (token, group), for groups that are a multiple of 4 columns: four columns a lane and
+// step, no shared memory, no barrier; the second pass finds its rows in L1.
+template <typename TY, typename T>
+__global__ void gated_norm_warp_kernel(const TY* __restrict__ y, int y_stride, const T* __restrict__ g, int g_stride,
+                                       int g_col0, int act, int gate_first, int norm, const float* __restrict__ weight,
+                                       int weight_period, float eps, T* __restrict__ out, int group, int groups,
+                                       long long total, int wide) {
+  pdl_trigger();
+  pdl_wait();
+  const long long index = blockIdx.x * static_cast<long long>(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (index >= total) return;
+  const int lane = threadIdx.x & 31;
+  const long long t = index / groups;
+  const int part = static_cast<int>(index - t * groups);
+  const TY* yr = y + static_cast<size_t>(t) * y_stride + static_cast<size_t>(part) * group;
+  const T* gr = (g && act != 0) ? g + static_cast<size_t>(t) * g_stride + g_col0 + static_cast<size_t>(part) * group : nullptr;
+  T* o = out + (static_cast<size_t>(t) * groups + part) * group;
+  auto load4 = [&](const auto* p, float (&v)[4]) {      // `wide`: every run of four starts on a vector's boundary
+    using E = std::remove_cv_t<std::remove_reference_t<decltype(*p)>>;
+    if (wide) {
+      if constexpr (sizeof(E) == 4) {
+        const float4 f = *reinterpret_cast<const float4*>(p);
+        v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+      } else {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        const float2 lo = __bfloat1622float2(h[0]), hi = __bfloat1622float2(h[1]);
+        v[0] = lo.x; v[1] = lo.y; v[2] = hi.x; v[3] = hi.y;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = to_float(p[j]);
+    }
+  };
+  auto four = [&](int i, float (&z)[4], float (&gate)[4]) {
+    load4(yr + i, z);
+    float raw[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (gr) load4(gr + i, raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      gate[j] = gr ? (act == 1 ? sigmoid_f(raw[j]) : silu_f(raw[j])) : 1.0f;
+      if (gate_first) z[j] *= gate[j];
+    }
+  };
+  float inv = 1.0f;
+  if (norm) {
+    float sum_sq = 0.0f;
+    for (int i = lane * 4; i < group; i += 128) {
+      float z[4], gate[4];
+      four(i, z, gate);
+      sum_sq += z[0] * z[0] + z[1] * z[1] + z[2] * z[2] + z[3] * z[3];
+    }
+    sum_sq = warp_sum(sum_sq);
+    inv = 1.0f / sqrtf(sum_sq / static_cast<float>(group) + eps);
+  }
+  for (int i = lane * 4; i < group; i += 128) {
+    float z[4], gate[4];
+    four(i, z, gate);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      z[j] *= inv;
+      if (norm && weight) z[j] *= weight[(part * group + i + j) % weight_period];
+      if (!gate_first) z[j] *= gate[j];
+    }
+    if (wide) {
+      if constexpr (sizeof(T) == 4) {
+        *reinterpret_cast<float4*>(o + i) = make_float4(z[0], z[1], z[2], z[3]);
+      } else {
+        uint2 packed;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+        h[0] = __floats2bfloat162_rn(z[0], z[1]);
+        h[1] = __floats2bfloat162_rn(z[2], z[3]);
+        *reinterpret_cast<uint2*>(o + i) = packed;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[i + j] = from_float<T>(z[j]);
+    }
+  }
+}
+
 // ------------------------------------------------------------ xIELU
 // z > 0: softplus(p) z^2 + z / 2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2;  pq = {p, q}.
 template <typename T>
-__global__ void xielu_kernel(const T* __restrict__ in, T* __restrict__ out, const float* __restrict__ pq, size_t n) {
+__global__ void xielu_kernel(const T* __restrict__ in, T* __restrict__ out, const float* __restrict__ pq, size_t n,
+                             int vector) {
   pdl_trigger();
   const float up = softplus_f(pq[0]), down = 0.5f + softplus_f(pq[1]);
   pdl_wait();
-  for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < n;
+  auto one = [&](float z) {
+    // exp(z) - 1 - z loses digits for small |z|, but beside z / 2 what is lost is below a sixteen-bit result's last
+    // place; the 32-bit engine takes expm1f
+    const float grown = sizeof(T) == 2 ? __expf(z) - 1.0f : expm1f(z);
+    return z > 0.0f ? up * z * z + 0.5f * z : down * (grown - z) + 0.5f * z;
+  };
+  const size_t quads = vector ? n >> 2 : 0;      // four at a time where both rows start on 16 bytes
+  for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < quads;
        idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const float z = to_float(in[idx]);
-    const float r = z > 0.0f ? up * z * z + 0.5f * z : down * (expm1f(z) - z) + 0.5f * z;
-    out[idx] = from_float<T>(r);
+    float z[4];
+    if constexpr (sizeof(T) == 2) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(in + idx * 4);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      const float2 lo = __bfloat1622float2(h[0]), hi = __bfloat1622float2(h[1]);
+      z[0] = lo.x; z[1] = lo.y; z[2] = hi.x; z[3] = hi.y;
+      uint2 packed;
+      __nv_bfloat162* ph = reinterpret_cast<__nv_bfloat162*>(&packed);
+      ph[0] = __floats2bfloat162_rn(one(z[0]), one(z[1]));
+      ph[1] = __floats2bfloat162_rn(one(z[2]), one(z[3]));
+      *reinterpret_cast<uint2*>(out + idx * 4) = packed;
+    } else {
+      const float4 v = *reinterpret_cast<const float4*>(in + idx * 4);
+      *reinterpret_cast<float4*>(out + idx * 4) = make_float4(one(v.x), one(v.y), one(v.z), one(v.w));
+    }
   }
+  for (size_t idx = (quads << 2) + blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < n;
+       idx += static_cast<size_t>(gridDim.x) * blockDim.x)
+    out[idx] = from_float<T>(one(to_float(in[idx])));
 }
 
 // weighted sum of two results: out = a_scale * a + b_scale * b (float32 arithmetic)
@@ -543,8 +717,15 @@ int rl_causal_conv_silu(int dtype, const void* x, int x_stride, int col0, const 
   if (tokens == 0 || channels == 0) return 0;
   if (width < 1 || width > rl::kMaxTaps || entries < 1) return static_cast<int>(cudaErrorInvalidValue);
   RL_DISPATCH_DTYPE(dtype, {
-    int code = rl::launch_kernel(rl::causal_conv_silu_kernel<scalar_t>,
-                                 dim3(rl::flat_blocks(static_cast<long long>(tokens) * channels, 256)), dim3(256), 0,
+    const bool pairs = channels % 2 == 0 && col0 % 2 == 0 && x_stride % 2 == 0 &&
+                       (reinterpret_cast<uintptr_t>(x) & 7) == 0 && (reinterpret_cast<uintptr_t>(out) & 7) == 0;
+    const long long tiles = (tokens + rl::kConvRows - 1) / rl::kConvRows;
+    const long long threads = tiles * (pairs ? channels / 2 : channels);
+    auto kernel = pairs ? rl::causal_conv_silu_kernel<scalar_t, 2, 0> : rl::causal_conv_silu_kernel<scalar_t, 1, 0>;
+    if (pairs && width == 4) kernel = rl::causal_conv_silu_kernel<scalar_t, 2, 4>;
+    if (pairs && width == 3) kernel = rl::causal_conv_silu_kernel<scalar_t, 2, 3>;
+    if (pairs && width == 2) kernel = rl::causal_conv_silu_kernel<scalar_t, 2, 2>;
+    int code = rl::launch_kernel(kernel, dim3(static_cast<unsigned>((threads + 127) / 128)), dim3(128), 0,
                                  stream, pdl != 0, static_cast<const scalar_t*>(x), x_stride, col0, taps, bias,
                                  static_cast<const float*>(state), state_stride, state_off, out, cu_seqlens,
                                  entry_slot, entry_start, entries, tokens, channels, width, slots, fault);
@@ -588,7 +769,7 @@ int rl_rotate_heads(int dtype, const void* in, int in_stride, int q_col0, int k_
   if (tokens == 0) return 0;
   if (rot < 0 || rot > dim || (rot & 1)) return static_cast<int>(cudaErrorInvalidValue);
   RL_DISPATCH_DTYPE(dtype, {
-    return rl::launch_kernel(rl::rotate_heads_kernel<scalar_t>, dim3(tokens), dim3(256), 0, stream, pdl != 0,
+    return rl::launch_kernel(rl::rotate_heads_kernel<scalar_t>, dim3(tokens), dim3(256), rot * sizeof(float), stream, pdl != 0,
                              static_cast<const scalar_t*>(in), in_stride, q_col0, k_col0, v_col0, out, positions,
                              inv_freq, heads, dim, vdim, rot, k_scale, tokens);
   });
@@ -644,6 +825,23 @@ int rl_gated_norm(int dtype, int y_f32, const void* y, int y_stride, const void*
   int threads = 32;
   while (threads < 256 && threads * 2 <= group) threads *= 2;
   const dim3 grid(tokens, groups), block(threads);
+  if (group % 4 == 0 && group <= 2048) {
+    const long long total = static_cast<long long>(tokens) * groups;
+    const dim3 warp_grid(static_cast<unsigned>((total + 7) / 8)), warp_block(256);
+    const bool wide = ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
+                      y_stride % 4 == 0 && g_stride % 4 == 0 && g_col0 % 4 == 0;
+    RL_DISPATCH_DTYPE(dtype, {
+      if (y_f32)
+        return rl::launch_kernel(rl::gated_norm_warp_kernel<float, scalar_t>, warp_grid, warp_block, 0, stream, pdl != 0,
+                                 static_cast<const float*>(y), y_stride, static_cast<const scalar_t*>(g), g_stride,
+                                 g_col0, act, gate_first, norm, weight, weight_period, eps,
+                                 static_cast<scalar_t*>(out), group, groups, total, static_cast<int>(wide));
+      return rl::launch_kernel(rl::gated_norm_warp_kernel<scalar_t, scalar_t>, warp_grid, warp_block, 0, stream, pdl != 0,
+                               static_cast<const scalar_t*>(y), y_stride, static_cast<const scalar_t*>(g), g_stride,
+                               g_col0, act, gate_first, norm, weight, weight_period, eps,
+                               static_cast<scalar_t*>(out), group, groups, total, static_cast<int>(wide));
+    });
+  }
   RL_DISPATCH_DTYPE(dtype, {
     if (y_f32)
       return rl::launch_kernel(rl::gated_norm_kernel<float, scalar_t>, grid, block, 0, stream, pdl != 0,
@@ -661,8 +859,9 @@ int rl_gated_norm(int dtype, int y_f32, const void* y, int y_stride, const void*
 int rl_xielu(int dtype, const void* in, void* out, const float* pq, long long n, int pdl, cudaStream_t stream) {
   if (n == 0) return 0;
   RL_DISPATCH_DTYPE(dtype, {
-    return rl::launch_kernel(rl::xielu_kernel<scalar_t>, dim3(rl::flat_blocks(n, 256)), dim3(256), 0, stream, pdl != 0,
-                             static_cast<const scalar_t*>(in), static_cast<scalar_t*>(out), pq, static_cast<size_t>(n));
+    return rl::launch_kernel(rl::xielu_kernel<scalar_t>, dim3(rl::flat_blocks((n + 3) / 4, 256)), dim3(256), 0, stream, pdl != 0,
+                             static_cast<const scalar_t*>(in), static_cast<scalar_t*>(out), pq, static_cast<size_t>(n),
+                             static_cast<int>(((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0));
   });
   return 0;
 }

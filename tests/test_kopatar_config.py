@@ -77,3 +77,23 @@ def test_the_plain_convolution_is_the_librarys():
     x, taps = torch.randn(9, 5, dtype=torch.float64), torch.randn(5, 3, dtype=torch.float64)
     want = torch.nn.functional.conv1d(torch.nn.functional.pad(x.T.unsqueeze(0), (2, 0)), taps.unsqueeze(1), groups=5)[0].T
     torch.testing.assert_close(causal_conv(x, taps), want)
+
+
+def test_random_init_writes_a_kopatar_folder_from_the_command_line(tmp_path):
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    config = tmp_path / "config.json"
+    config.write_text(json.dumps(CONFIGS["loop_inside"]))
+    done = subprocess.run([sys.executable, "-m", "rapid_llm_b200.cli", "random-init", "--config", str(config), "--out",
+                           str(tmp_path / "model"), "--seed", "4"], cwd=root, capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr
+    loaded = load_config(tmp_path / "model")
+    assert isinstance(loaded, KopatarConfig) and loaded.loop == CONFIGS["loop_inside"]["loop"]
+    from rapid_llm_b200.weights import SafetensorsFile
+
+    with SafetensorsFile(tmp_path / "model" / "model.safetensors") as handle:
+        assert set(handle.keys()) == set(tensor_shapes(CONFIGS["loop_inside"]))

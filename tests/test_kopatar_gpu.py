@@ -212,3 +212,40 @@ def test_zz_report_the_errors_seen(capsys):
         for label, worst in sorted(WORST.items()):
             if "bfloat16" in label:
                 print(f"\n  {label}: {worst:.4f}", end="")
+
+
+def test_the_command_line_and_the_trace_runner_take_a_kopatar_folder(tmp_path):
+    """``batch`` generates from token-id prompts; ``bin/trace_run`` replays steps and writes the same logits as the
+    plain implementation computes."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    import numpy as np
+
+    root = Path(__file__).resolve().parents[1]
+    config = CONFIGS["loop_inside"]
+    weights = make_weights(config, seed=23)
+    folder = write_folder(tmp_path / "model", config, weights, torch.float32)
+    prompts = tmp_path / "prompts.txt"
+    prompts.write_text("5 9 12 80 3\n7 7 1\n")
+    done = subprocess.run([sys.executable, "-m", "rapid_llm_b200.cli", "batch", "--model-dir", str(folder), "--dtype", "float32",
+                           "--prompt-ids-file", str(prompts), "--max-gen-len", "6", "--temperature", "0", "--repetition-penalty", "1.0", "--max-seq-len", "64",
+                           "--max-gpu-num-blocks", "16"], cwd=root, capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr
+    lines = [line for line in done.stdout.splitlines() if line and not line.startswith("---")]
+    assert [int(t) for t in lines[0].split()] == greedy(config, as_double(weights), [5, 9, 12, 80, 3], 6)
+
+    tokens = _sequences(config, [30], seed=2)["r0"]
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": tokens[:17], "want": [16]}], "end": []},
+             {"step": 1, "entries": [{"id": "x", "tokens": tokens[17:], "want": [0, 12]}], "end": ["x"]}]
+    out = tmp_path / "out"
+    done = subprocess.run([str(root / "bin" / "trace_run"), "--model", str(folder), "--dtype", "float32", "--out", str(out),
+                           "--max-tokens", "64"], input="".join(json.dumps(s) + "\n" for s in steps), cwd=tmp_path,
+                          capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr
+    assert [line for line in done.stdout.splitlines() if line.startswith("done")] == ["done 0", "done 1"]
+    plain = forward(config, as_double(weights), tokens).float()
+    got = torch.from_numpy(np.fromfile(out / "1.f32", dtype="<f4").reshape(2, -1).copy())
+    assert_rows_close_by_size(got, plain[[17, 29]], "float32")
