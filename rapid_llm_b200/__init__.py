@@ -1,4 +1,4 @@
-"""A B200-native inference engine for the Qwen3 dense decoder.
+"""A B200-native inference engine for the Qwen3 dense decoder and the recurrent Kopatar decoder.
 
 ``LLM(model_dir).generate(prompts, SamplingParams(...))`` is the Python entry point;
 ``bin/trace_run`` replays given token ids and writes logits; ``python -m rapid_llm_b200.cli``
@@ -7,7 +7,7 @@ is the command line.
 
 __version__ = "0.1.0"
 
-from .config import EngineConfig, Qwen3Config, load_config
+from .config import EngineConfig, KopatarConfig, Qwen3Config, load_config
 from .sampling.params import SamplingParams
 
 
@@ -27,4 +27,4 @@ def __getattr__(name):  # the engine imports lazily: configuration and weights w
     raise AttributeError(name)
 
 
-__all__ = ["EngineConfig", "LLM", "ModelRunner", "Qwen3Config", "SamplingParams", "Scheduler", "load_config"]
+__all__ = ["EngineConfig", "KopatarConfig", "LLM", "ModelRunner", "Qwen3Config", "SamplingParams", "Scheduler", "load_config"]
