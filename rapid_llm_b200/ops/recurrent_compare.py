@@ -3,6 +3,7 @@ and every kernel of the recurrent mixers alone against the memory roofline.
 
     python bench.py --workload kopatar [--sizes 2048,4096]
     python -m rapid_llm_b200.ops.recurrent_compare [--sizes 2048,4096]
+    python -m rapid_llm_b200.ops.recurrent_compare --scan fixed|delta      # three launches of the recurrence, for ncu
 
 Random weights, bfloat16, one GPU.  A model of width ``W`` has heads of 128, a feed-forward of ``4 W`` (Qwen3's
 gated one gets ``8 W / 3`` rounded to 256, the same number of weights) and the layers
@@ -183,6 +184,30 @@ def kernel_figures(width: int, hbm_gbs: float) -> dict:
     return out
 
 
+def scan_alone(kind: str, width: int = 2048, launches: int = 3) -> None:
+    """A few launches of the recurrence kernel over one 2,048-token prompt and nothing else: the case a profiler
+    captures (``--scan fixed`` or ``--scan delta``)."""
+    from . import kernels
+
+    device, heads, dim, tokens = "cuda:0", width // 128, 128, PREFILL
+    c = heads * dim
+    batch = SimpleNamespace(
+        cu_seqlens=torch.tensor([0, tokens], dtype=torch.int32, device=device),
+        entry_slot=torch.zeros(1, dtype=torch.int32, device=device),
+        entry_start=torch.full((1,), 512, dtype=torch.int32, device=device), num_entries=1,
+        fault=torch.zeros(1, dtype=torch.int32, device=device))
+    q, k, v, read = (torch.randn(tokens, c, device=device) for _ in range(4))
+    state = torch.zeros(1, heads * dim * dim, device=device)
+    for _ in range(launches):
+        if kind == "delta":
+            kernels.linear_scan(q, k, v, torch.rand(tokens, c, device=device), read, state, batch, heads=heads,
+                                kv_heads=heads, dim=dim, vdim=dim, beta=torch.rand(tokens, heads, device=device))
+        else:
+            kernels.linear_scan(q, k, v, torch.rand(heads, device=device), read, state, batch, heads=heads,
+                                kv_heads=heads, dim=dim, vdim=dim)
+    torch.cuda.synchronize()
+
+
 def run(sizes: list[int], hbm_gbs: float) -> dict:
     from ..config import KopatarConfig, Qwen3Config
 
@@ -201,7 +226,12 @@ def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__.splitlines()[0])
     parser.add_argument("--sizes", default="2048,4096")
     parser.add_argument("--hbm-gbs", type=float, default=6650.0)
+    parser.add_argument("--scan", choices=["fixed", "delta"], default=None,
+                        help="only launch the recurrence kernel a few times (for a profiler)")
     args = parser.parse_args()
+    if args.scan:
+        scan_alone(args.scan)
+        return 0
     print(json.dumps(run([int(s) for s in args.sizes.split(",") if s], args.hbm_gbs)))
     return 0
 
