@@ -72,7 +72,7 @@ template <typename TX, typename TOut, bool kVector>
 __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, float* __restrict__ residual,
                                    const float* __restrict__ weight, TOut* __restrict__ out,
                                    const int* __restrict__ row_index, int hidden, float eps,
-                                   int mode, int write_residual, const TX* __restrict__ extra_rows,
+                                   int mode, int write_residual, const TX* extra_rows,
                                    const float* __restrict__ extra_vector) {
   extern __shared__ float row_values[];  // [hidden] on the element-by-element path
   __shared__ float scratch[32];

@@ -9,6 +9,11 @@
 // recurrence consumes (decays, step sizes, gates, unit vectors, the state) is float32 in both engine
 // precisions; the recurrence runs token by token in a fixed order, so a row's result does not depend
 // on how the tokens were cut into steps or on what else is in the batch.
+//
+// Pointers to what an earlier kernel of the same step wrote (activations, the state) carry no `__restrict__`:
+// a load through a const restrict pointer counts as invariant and may be moved above the wait for the
+// kernel before (seen: a convolution that read its rows before the product that writes them had finished,
+// once its loads no longer depended on anything else).  Weights and the step's uploaded metadata keep it.
 #include <type_traits>
 
 #include "common.cuh"
@@ -51,9 +56,9 @@ __device__ __forceinline__ float2 load_pair<__nv_bfloat16>(const __nv_bfloat16* 
 // window down them, so a row of x is fetched once, not once per tap.  kLanes == 2 wants even C, col0 and x_stride.
 // kTaps > 0: the taps' number is known when compiling and the window lives in registers; 0: any number up to kMaxTaps.
 template <typename T, int kLanes, int kTaps>
-__global__ void causal_conv_silu_kernel(const T* __restrict__ x, int x_stride, int col0,
+__global__ void causal_conv_silu_kernel(const T* x, int x_stride, int col0,
                                         const float* __restrict__ taps, const float* __restrict__ bias,
-                                        const float* __restrict__ state, long long state_stride, int state_off,
+                                        const float* state, long long state_stride, int state_off,
                                         float* __restrict__ out, const int* __restrict__ cu_seqlens,
                                         const int* __restrict__ entry_slot, const int* __restrict__ entry_start,
                                         int entries, int tokens, int C, int taps_given, int slots, int* __restrict__ fault) {
@@ -79,10 +84,26 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ x, int x_stride, i
   const int t0 = tile * kConvRows;
   int e = entry_of(cu_seqlens, entries, t0);
   pdl_wait();
+  // this tile's own rows, asked for at once (every row needs its own input, whatever entry it belongs to)
+  float own[kLanes][kConvRows];
+#pragma unroll
+  for (int r = 0; r < kConvRows; ++r) {
+    if (t0 + r < tokens) {
+      if constexpr (kLanes == 2) {
+        const float2 v = load_pair(x + static_cast<size_t>(t0 + r) * x_stride + col0 + c);
+        own[0][r] = v.x; own[1][r] = v.y;
+      } else {
+        own[0][r] = to_float(x[static_cast<size_t>(t0 + r) * x_stride + col0 + c]);
+      }
+    }
+  }
   // the window: hist[d] is the input d rows back (hist[0] the current row's)
   float hist[kLanes][kHeld];
   int filled_for = -1;      // the entry the window was filled for
-  for (int t = t0; t < min(t0 + kConvRows, tokens); ++t) {
+#pragma unroll
+  for (int r = 0; r < kConvRows; ++r) {
+    const int t = t0 + r;
+    if (t >= tokens) break;
     while (t >= cu_seqlens[e + 1]) ++e;
     const int local = t - cu_seqlens[e], start = entry_start[e];
     if (filled_for != e) {      // first row of this tile that belongs to entry e: fetch the K - 1 inputs before it
@@ -112,12 +133,8 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ x, int x_stride, i
       }
       filled_for = e;
     }
-    if constexpr (kLanes == 2) {
-      const float2 v = load_pair(x + static_cast<size_t>(t) * x_stride + col0 + c);
-      hist[0][0] = v.x; hist[1][0] = v.y;
-    } else {
-      hist[0][0] = to_float(x[static_cast<size_t>(t) * x_stride + col0 + c]);
-    }
+#pragma unroll
+    for (int l = 0; l < kLanes; ++l) hist[l][0] = own[l][r];
     float acc[kLanes];
 #pragma unroll
     for (int l = 0; l < kLanes; ++l) {
@@ -144,7 +161,7 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ x, int x_stride, i
 // The slot's tail after the step: the last K - 1 inputs of the request, taken from this step's rows
 // and, where the step brought fewer, from the old tail.  A thread reads all it needs before it writes.
 template <typename T>
-__global__ void conv_tail_update_kernel(const T* __restrict__ x, int x_stride, int col0,
+__global__ void conv_tail_update_kernel(const T* x, int x_stride, int col0,
                                         float* __restrict__ state, long long state_stride, int state_off,
                                         const int* __restrict__ cu_seqlens, const int* __restrict__ entry_slot,
                                         const int* __restrict__ entry_start, int entries, int C, int K, int slots) {
@@ -174,20 +191,46 @@ __global__ void conv_tail_update_kernel(const T* __restrict__ x, int x_stride, i
 }
 
 // ------------------------------------------------------------ decays and step sizes
-// step[t, c] = softplus(x[t, c] + bias[c]); decay[t, c] = exp(-exp(a_log[c / per]) * step[t, c]).
-template <typename T>
-__global__ void decay_gate_kernel(const T* __restrict__ x, int x_stride, int col0, const float* __restrict__ a_log,
+// step[t, c] = softplus(x[t, c] + bias[c]); decay[t, c] = exp(-rate[c / per] * step[t, c]), rate = exp(A_log)
+// (taken once when the weights are loaded).  kWide: four columns a thread, 8- and 16-byte accesses.
+template <typename T, bool kWide>
+__global__ void decay_gate_kernel(const T* x, int x_stride, int col0, const float* __restrict__ rate,
                                   const float* __restrict__ bias, int per, float* __restrict__ decay,
                                   float* __restrict__ step, int tokens, int C) {
   pdl_trigger();
   pdl_wait();
-  const long long total = static_cast<long long>(tokens) * C;
+  constexpr int kEach = kWide ? 4 : 1;
+  const int per_row = C / kEach;
+  const long long total = static_cast<long long>(tokens) * per_row;
   for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
        idx += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int t = static_cast<int>(idx / C), c = static_cast<int>(idx - static_cast<long long>(t) * C);
-    const float dt = softplus_f(to_float(x[static_cast<size_t>(t) * x_stride + col0 + c]) + (bias ? bias[c] : 0.0f));
-    decay[idx] = expf(-expf(a_log[c / per]) * dt);
-    if (step) step[idx] = dt;
+    const int t = static_cast<int>(idx / per_row), c = static_cast<int>(idx - static_cast<long long>(t) * per_row) * kEach;
+    const T* in = x + static_cast<size_t>(t) * x_stride + col0 + c;
+    float raw[kEach], dt[kEach], d[kEach];
+    if constexpr (kWide && sizeof(T) == 2) {
+      const uint2 packed = *reinterpret_cast<const uint2*>(in);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&packed);
+      const float2 lo = __bfloat1622float2(h[0]), hi = __bfloat1622float2(h[1]);
+      raw[0] = lo.x; raw[1] = lo.y; raw[2] = hi.x; raw[3] = hi.y;
+    } else if constexpr (kWide) {
+      const float4 f = *reinterpret_cast<const float4*>(in);
+      raw[0] = f.x; raw[1] = f.y; raw[2] = f.z; raw[3] = f.w;
+    } else {
+      raw[0] = to_float(in[0]);
+    }
+#pragma unroll
+    for (int j = 0; j < kEach; ++j) {
+      dt[j] = softplus_f(raw[j] + (bias ? bias[c + j] : 0.0f));
+      d[j] = expf(-rate[(c + j) / per] * dt[j]);
+    }
+    float* to = decay + static_cast<size_t>(t) * C + c;
+    if constexpr (kWide) {
+      *reinterpret_cast<float4*>(to) = make_float4(d[0], d[1], d[2], d[3]);
+      if (step) *reinterpret_cast<float4*>(step + static_cast<size_t>(t) * C + c) = make_float4(dt[0], dt[1], dt[2], dt[3]);
+    } else {
+      to[0] = d[0];
+      if (step) step[static_cast<size_t>(t) * C + c] = dt[0];
+    }
   }
 }
 
@@ -197,7 +240,7 @@ __global__ void decay_gate_kernel(const T* __restrict__ x, int x_stride, int col
 // Beside it, sigmoid of `gates` columns of a row of the engine's dtype into a float32 [T, gates].
 template <typename T>
 __global__ void unit_heads_kernel(float* __restrict__ rows, int stride, int col0, int heads, int dim, float eps,
-                                  int split, float scale_low, float scale_high, const T* __restrict__ gate_in,
+                                  int split, float scale_low, float scale_high, const T* gate_in,
                                   int gate_stride, int gate_col0, int gates, float* __restrict__ gate_out, int tokens) {
   pdl_trigger();
   pdl_wait();
@@ -223,11 +266,11 @@ __global__ void unit_heads_kernel(float* __restrict__ rows, int stride, int col0
 // their first `rot` entries rotated by position (entry i paired with i + rot / 2, angle = position *
 // inv_freq[i], all float32), k times k_scale after the rotation.
 template <typename T>
-__global__ void rotate_heads_kernel(const T* __restrict__ in, int in_stride, int q_col0, int k_col0, int v_col0,
+__global__ void rotate_heads_kernel(const T* in, int in_stride, int q_col0, int k_col0, int v_col0,
                                     float* __restrict__ out, const int* __restrict__ positions,
                                     const float* __restrict__ inv_freq, int heads, int dim, int vdim, int rot,
-                                    float k_scale, int tokens) {
-  extern __shared__ float angles[];      // cos, then sin, of the token's rot / 2 angles: the same for every head
+                                    float k_scale, int tokens, int wide) {
+  extern __shared__ __align__(16) float angles[];      // cos, then sin, of the token's rot / 2 angles: the same for every head
   pdl_trigger();
   const int t = blockIdx.x;
   const int qk = heads * dim, half = rot >> 1;
@@ -237,6 +280,56 @@ __global__ void rotate_heads_kernel(const T* __restrict__ in, int in_stride, int
   __syncthreads();
   const T* row = in + static_cast<size_t>(t) * in_stride;
   float* o = out + static_cast<size_t>(t) * (2 * qk + heads * vdim);
+  if (wide) {
+    // four neighbouring entries of a head and their partners at once: every input is read once, 8 or 16 bytes at a time
+    auto load4 = [](const T* p, float (&v)[4]) {
+      if constexpr (sizeof(T) == 2) {
+        const uint2 packed = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&packed);
+        const float2 lo = __bfloat1622float2(h[0]), hi = __bfloat1622float2(h[1]);
+        v[0] = lo.x; v[1] = lo.y; v[2] = hi.x; v[3] = hi.y;
+      } else {
+        const float4 f = *reinterpret_cast<const float4*>(p);
+        v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+      }
+    };
+    const int quads_rot = half >> 2, quads_rest = (dim - rot) >> 2, per_head = quads_rot + quads_rest;
+    for (int idx = threadIdx.x; idx < 2 * heads * per_head; idx += blockDim.x) {
+      const int head2 = idx / per_head, j = idx - head2 * per_head;      // head2: query heads, then key heads
+      const bool is_k = head2 >= heads;
+      const int head = is_k ? head2 - heads : head2;
+      const T* src = row + (is_k ? k_col0 : q_col0) + head * dim;
+      float* dst = o + (is_k ? qk : 0) + head * dim;
+      const float scale = is_k ? k_scale : 1.0f;
+      if (j < quads_rot) {
+        const int i = j << 2;
+        float x1[4], x2[4];
+        load4(src + i, x1);
+        load4(src + i + half, x2);
+        const float4 c = *reinterpret_cast<const float4*>(angles + i), sn = *reinterpret_cast<const float4*>(angles + half + i);
+        const float cs[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+        float o1[4], o2[4];
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+          o1[n] = (x1[n] * cs[n] - x2[n] * ss[n]) * scale;
+          o2[n] = (x2[n] * cs[n] + x1[n] * ss[n]) * scale;
+        }
+        *reinterpret_cast<float4*>(dst + i) = make_float4(o1[0], o1[1], o1[2], o1[3]);
+        *reinterpret_cast<float4*>(dst + i + half) = make_float4(o2[0], o2[1], o2[2], o2[3]);
+      } else {
+        const int i = rot + ((j - quads_rot) << 2);
+        float v[4];
+        load4(src + i, v);
+        *reinterpret_cast<float4*>(dst + i) = make_float4(v[0] * scale, v[1] * scale, v[2] * scale, v[3] * scale);
+      }
+    }
+    for (int idx = threadIdx.x * 4; idx < heads * vdim; idx += blockDim.x * 4) {
+      float v[4];
+      load4(row + v_col0 + idx, v);
+      *reinterpret_cast<float4*>(o + 2 * qk + idx) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+    return;
+  }
   for (int idx = threadIdx.x; idx < 2 * qk; idx += blockDim.x) {
     const bool is_k = idx >= qk;
     const int within = is_k ? idx - qk : idx;
@@ -532,7 +625,7 @@ __global__ void __launch_bounds__(kScanThreads) linear_scan_kernel(const ScanArg
 // divides a group by sqrt(mean(z^2) + eps) and multiplies by weight[c % weight_period] (or nothing).
 // One block per (token, group); float32 arithmetic, one rounding at the store.
 template <typename TY, typename T>
-__global__ void gated_norm_kernel(const TY* __restrict__ y, int y_stride, const T* __restrict__ g, int g_stride,
+__global__ void gated_norm_kernel(const TY* y, int y_stride, const T* g, int g_stride,
                                   int g_col0, int act, int gate_first, int norm, const float* __restrict__ weight,
                                   int weight_period, float eps, T* __restrict__ out, int group, int groups) {
   __shared__ float scratch[32];
@@ -572,7 +665,7 @@ __global__ void gated_norm_kernel(const TY* __restrict__ y, int y_stride, const 
 // The same with one warp per (token, group), for groups that are a multiple of 4 columns: four columns a lane and
 // step, no shared memory, no barrier; the second pass finds its rows in L1.
 template <typename TY, typename T>
-__global__ void gated_norm_warp_kernel(const TY* __restrict__ y, int y_stride, const T* __restrict__ g, int g_stride,
+__global__ void gated_norm_warp_kernel(const TY* y, int y_stride, const T* g, int g_stride,
                                        int g_col0, int act, int gate_first, int norm, const float* __restrict__ weight,
                                        int weight_period, float eps, T* __restrict__ out, int group, int groups,
                                        long long total, int wide) {
@@ -653,7 +746,7 @@ __global__ void gated_norm_warp_kernel(const TY* __restrict__ y, int y_stride, c
 // ------------------------------------------------------------ xIELU
 // z > 0: softplus(p) z^2 + z / 2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2;  pq = {p, q}.
 template <typename T>
-__global__ void xielu_kernel(const T* __restrict__ in, T* __restrict__ out, const float* __restrict__ pq, size_t n,
+__global__ void xielu_kernel(const T* in, T* __restrict__ out, const float* __restrict__ pq, size_t n,
                              int vector) {
   pdl_trigger();
   const float up = softplus_f(pq[0]), down = 0.5f + softplus_f(pq[1]);
@@ -690,7 +783,7 @@ __global__ void xielu_kernel(const T* __restrict__ in, T* __restrict__ out, cons
 
 // weighted sum of two results: out = a_scale * a + b_scale * b (float32 arithmetic)
 template <typename T>
-__global__ void scaled_sum_kernel(const T* __restrict__ a, const T* __restrict__ b, float a_scale, float b_scale,
+__global__ void scaled_sum_kernel(const T* a, const T* b, float a_scale, float b_scale,
                                   T* __restrict__ out, size_t n) {
   pdl_trigger();
   pdl_wait();
@@ -738,15 +831,17 @@ int rl_causal_conv_silu(int dtype, const void* x, int x_stride, int col0, const 
   return 0;
 }
 
-int rl_decay_gate(int dtype, const void* x, int x_stride, int col0, const float* a_log, const float* bias, int per,
+int rl_decay_gate(int dtype, const void* x, int x_stride, int col0, const float* rate, const float* bias, int per,
                   float* decay, float* step, int tokens, int channels, int pdl, cudaStream_t stream) {
   if (tokens == 0 || channels == 0) return 0;
   if (per < 1) return static_cast<int>(cudaErrorInvalidValue);
+  const bool wide = channels % 4 == 0 && x_stride % 4 == 0 && col0 % 4 == 0 &&
+                    ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(decay) | reinterpret_cast<uintptr_t>(step)) & 15) == 0;
   RL_DISPATCH_DTYPE(dtype, {
-    return rl::launch_kernel(rl::decay_gate_kernel<scalar_t>,
-                             dim3(rl::flat_blocks(static_cast<long long>(tokens) * channels, 256)), dim3(256), 0, stream,
-                             pdl != 0, static_cast<const scalar_t*>(x), x_stride, col0, a_log, bias, per, decay, step,
-                             tokens, channels);
+    auto kernel = wide ? rl::decay_gate_kernel<scalar_t, true> : rl::decay_gate_kernel<scalar_t, false>;
+    return rl::launch_kernel(kernel, dim3(rl::flat_blocks(static_cast<long long>(tokens) * channels / (wide ? 4 : 1), 256)),
+                             dim3(256), 0, stream, pdl != 0, static_cast<const scalar_t*>(x), x_stride, col0, rate, bias,
+                             per, decay, step, tokens, channels);
   });
   return 0;
 }
@@ -768,10 +863,13 @@ int rl_rotate_heads(int dtype, const void* in, int in_stride, int q_col0, int k_
                     int tokens, int pdl, cudaStream_t stream) {
   if (tokens == 0) return 0;
   if (rot < 0 || rot > dim || (rot & 1)) return static_cast<int>(cudaErrorInvalidValue);
+  const bool wide = rot % 8 == 0 && dim % 4 == 0 && vdim % 4 == 0 && in_stride % 4 == 0 && q_col0 % 4 == 0 &&
+                    k_col0 % 4 == 0 && v_col0 % 4 == 0 &&
+                    ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
   RL_DISPATCH_DTYPE(dtype, {
     return rl::launch_kernel(rl::rotate_heads_kernel<scalar_t>, dim3(tokens), dim3(256), rot * sizeof(float), stream, pdl != 0,
                              static_cast<const scalar_t*>(in), in_stride, q_col0, k_col0, v_col0, out, positions,
-                             inv_freq, heads, dim, vdim, rot, k_scale, tokens);
+                             inv_freq, heads, dim, vdim, rot, k_scale, tokens, static_cast<int>(wide));
   });
   return 0;
 }

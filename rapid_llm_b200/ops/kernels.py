@@ -877,11 +877,13 @@ def causal_conv_silu(x: torch.Tensor, taps: torch.Tensor, bias: torch.Tensor | N
     return out
 
 
-def decay_gate(x: torch.Tensor, a_log: torch.Tensor, bias: torch.Tensor | None, per: int, decay: torch.Tensor,
+def decay_gate(x: torch.Tensor, rate: torch.Tensor, bias: torch.Tensor | None, per: int, decay: torch.Tensor,
                step: torch.Tensor | None = None) -> torch.Tensor:
-    """``step = softplus(x + bias)``, ``decay = exp(-exp(a_log[c // per]) * step)``; float32 results ``[T, C]``."""
+    """``step = softplus(x + bias)``, ``decay = exp(-rate[c // per] * step)``; float32 results ``[T, C]``.
+    ``rate`` is ``exp(A_log)`` (float32), which a mixer takes once when its weights are loaded."""
+    a_log = rate
     _need_cuda(x, a_log, bias, decay, step)
-    for name, tensor in (("a_log", a_log), ("bias", bias), ("decay", decay), ("step", step)):
+    for name, tensor in (("rate", a_log), ("bias", bias), ("decay", decay), ("step", step)):
         _expect(name, tensor, torch.float32), _contig(name, tensor)
     tokens, channels = x.shape
     if decay.shape != (tokens, channels) or (step is not None and step.shape != decay.shape) \

@@ -55,6 +55,11 @@ class _Recurrent(Mixer):
     def parameter_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self._tensors())
 
+    def finalize(self, loaded: set[str]) -> None:
+        """The decay's rate ``exp(A_log)`` (float32) is taken once here, for the mixers that have one."""
+        if hasattr(self, "a_log"):
+            self.rate = torch.exp(self.a_log)
+
 
 @MIXERS.register("gated_delta_rule")
 class ChannelDeltaRule(_Recurrent):
@@ -162,7 +167,7 @@ class ChannelDeltaRule(_Recurrent):
         kernels.unit_heads(conv[:, : 2 * self.cq], heads=2 * self.hk, dim=self.dim, eps=self.unit_eps, split=self.hk,
                            scale_low=self.dim ** -0.5, scale_high=1.0, gate_in=proj[:, self.conv_channels :], gate_out=beta)
         decay = space.get("delta_decay", rows, self.h * self.dim, f32)
-        kernels.decay_gate(high[:, : self.h * self.dim], self.a_log, self.dt_bias, self.dim, decay)
+        kernels.decay_gate(high[:, : self.h * self.dim], self.rate, self.dt_bias, self.dim, decay)
         read = space.get("delta_read", rows, self.cv, f32)
         kernels.linear_scan(conv[:, : self.cq], conv[:, self.cq : 2 * self.cq], conv[:, 2 * self.cq :], decay, read, S,
                             batch, heads=self.h, kv_heads=self.hk, dim=self.dim, vdim=self.vdim, beta=beta)
@@ -322,7 +327,7 @@ class StateSpaceDual(_Recurrent):
         conv = space.get("ssd_conv", rows, mixed, f32)
         kernels.causal_conv_silu(proj[:, inner : inner + mixed], self.taps, self.conv_bias, tail, conv, batch)
         decay, step = space.get("ssd_decay", rows, self.h, f32), space.get("ssd_step", rows, self.h, f32)
-        kernels.decay_gate(proj[:, inner + mixed :], self.a_log, self.dt_bias, 1, decay, step)
+        kernels.decay_gate(proj[:, inner + mixed :], self.rate, self.dt_bias, 1, decay, step)
         read = space.get("ssd_read", rows, inner, f32)
         kernels.linear_scan(conv[:, inner + gn :], conv[:, inner : inner + gn], conv[:, :inner], decay, read, S, batch,
                             heads=self.h, kv_heads=self.groups, dim=self.n, vdim=self.vdim, v_scale=step, skip=self.skip)

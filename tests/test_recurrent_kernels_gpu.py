@@ -176,7 +176,7 @@ def test_activation_decays_unit_heads_and_rotation():
     x = torch.randn(tokens, heads * per + 2, generator=generator) * 2
     a_log, bias = torch.randn(heads, generator=generator), torch.randn(heads * per, generator=generator)
     decay, step = torch.empty(tokens, heads * per, device=DEV), torch.empty(tokens, heads * per, device=DEV)
-    kernels.decay_gate(x.to(DEV)[:, 2:], a_log.to(DEV), bias.to(DEV), per, decay, step)
+    kernels.decay_gate(x.to(DEV)[:, 2:], torch.exp(a_log).to(DEV), bias.to(DEV), per, decay, step)
     dt = softplus(x[:, 2:].double() + bias.double())
     torch.testing.assert_close(step.cpu().double(), dt, rtol=1e-5, atol=1e-6)
     torch.testing.assert_close(decay.cpu().double(), torch.exp(-torch.exp(a_log.double()).repeat_interleave(per) * dt), rtol=1e-5, atol=1e-6)
