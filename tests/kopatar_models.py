@@ -35,9 +35,10 @@ def delta_layer(*, heads=4, kv_heads=2, dim=16, vdim=24, conv=3, ff=None):
 
 
 def retention_layer(*, heads=2, dim=32, vdim=16, decay=(0.9, 0.999), rot_dims=8, base=100.0, ff=40):
-    return {"type": "retention",
-            "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "decay": list(decay), "rot": {"dims": rot_dims, "base": base}},
-            "mlp": None if ff is None else {"kind": "dense", "ff": ff}}
+    mixer = {"heads": heads, "dim": dim, "vdim": vdim, "decay": list(decay)}
+    if rot_dims:
+        mixer["rot"] = {"dims": rot_dims, "base": base}
+    return {"type": "retention", "mixer": mixer, "mlp": None if ff is None else {"kind": "dense", "ff": ff}}
 
 
 def make_config(layers, *, width=64, vocab=97, eps=1e-5, loop=None, ranks=(5, 7)) -> dict:
@@ -61,6 +62,13 @@ CONFIGS = {
         retention_layer(heads=3, dim=8, vdim=20, decay=(0.5, 0.97, 1.0), rot_dims=8, ff=None),
         delta_layer(heads=2, kv_heads=1, dim=40, vdim=8, conv=2, ff=36),
     ], width=60, vocab=130, ranks=(3, 4)),
+    # nothing is a multiple of 4: every kernel's element-by-element path; a convolution of one tap; no rotation
+    "narrow": make_config([
+        delta_layer(heads=3, kv_heads=3, dim=10, vdim=6, conv=2, ff=30),
+        parallel_layer(heads=2, kv_heads=1, dim=10, vdim=14, window=7, ssm_heads=3, ssm_vdim=5, state=7, groups=3,
+                       conv=1, norm_groups=1, ff=None),
+        retention_layer(heads=3, dim=6, vdim=9, decay=(0.8, 0.9, 0.99), rot_dims=0, ff=22),
+    ], width=50, vocab=83, ranks=(3, 3), loop=(2, 3, 2)),
     # a loop that starts at the first layer and runs three times, layers before and after none
     "loop_from_start": make_config([retention_layer(decay=(0.95, 0.99)), delta_layer(ff=40)], loop=(0, 2, 3)),
     # a loop in the middle, a parallel layer inside it (pages per pass), layers on both sides
