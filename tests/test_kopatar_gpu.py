@@ -206,12 +206,11 @@ def test_greedy_generation_through_the_entry_point(tmp_path):
         assert output.outputs[0].token_ids == greedy(config, as_double(weights), prompt, 12)
 
 
-def test_zz_report_the_errors_seen(capsys):
-    """Not a check: prints the largest bfloat16 row error of every comparison above (``pytest -s``)."""
-    with capsys.disabled():
-        for label, worst in sorted(WORST.items()):
-            if "bfloat16" in label:
-                print(f"\n  {label}: {worst:.4f}", end="")
+def test_zz_report_the_errors_seen():
+    """Not a check: prints the largest bfloat16 row error of every comparison above (shown with ``pytest -s``)."""
+    for label, worst in sorted(WORST.items()):
+        if "bfloat16" in label:
+            print(f"  {label}: {worst:.4f}")
 
 
 def test_the_command_line_and_the_trace_runner_take_a_kopatar_folder(tmp_path):
