@@ -3,6 +3,7 @@
 from .engine_config import EngineConfig, parse_dtype
 from .model_spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from .kopatar import KopatarConfig
+from .mezadra import MezadraConfig
 from .qwen3 import Qwen3Config
 from .registry import (
     load_config,
@@ -14,11 +15,13 @@ from .registry import (
 
 register_architecture(Qwen3Config)
 register_architecture(KopatarConfig)
+register_architecture(MezadraConfig)
 
 __all__ = [
     "EngineConfig",
     "KopatarConfig",
     "LayerSpec",
+    "MezadraConfig",
     "ModelSpec",
     "PartSpec",
     "Qwen3Config",

@@ -29,7 +29,7 @@ __global__ void attention_generic_kernel(
     const int* __restrict__ token_slot, // [tokens]
     const int* __restrict__ block_table,  // [slots, max_pages]
     int tokens, int hq, int hkv, int d, int page_size, int num_pages, int max_pages, int slots,
-    int window, float scale, int* __restrict__ fault) {
+    int window, float scale, float softcap, const float* __restrict__ sink, int* __restrict__ fault) {
   __shared__ float q_staged[kGenericWarps][kGenericMaxD];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = static_cast<long long>(blockIdx.x) * kGenericWarps + warp;
@@ -81,7 +81,8 @@ __global__ void attention_generic_kernel(
 #pragma unroll
           for (int e = 0; e < 8; ++e) dot = fmaf(qs[i + e], kv[e], dot);
         }
-        score = dot;
+        // squashed scores: cap * tanh(s / cap) of the scaled score, where the mixer has a cap
+        score = softcap > 0.0f ? softcap * tanhf(dot / softcap) : dot;
       }
     }
     const float chunk_max = warp_max(score);
@@ -106,7 +107,14 @@ __global__ void attention_generic_kernel(
       }
     }
   }
-  const float inv_sum = running_sum > 0.0f ? 1.0f / running_sum : 0.0f;
+  float inv_sum = running_sum > 0.0f ? 1.0f / running_sum : 0.0f;
+  if (sink != nullptr) {
+    // one more term exp(sink[head]) in the denominator, without a key or a value; it is neither scaled nor capped
+    const float s = sink[head];
+    const float top = fmaxf(running_max, s);
+    const float keys = running_max == -INFINITY ? 0.0f : expf(running_max - top);
+    inv_sum = keys / (running_sum * keys + expf(s - top));
+  }
 #pragma unroll
   for (int i = 0; i < kGenericMaxD / 32; ++i) {
     const int col = lane + 32 * i;
@@ -120,10 +128,11 @@ extern "C" int rl_attention_generic(int dtype, const void* q, const void* cache,
                                     const int* positions, const int* token_slot,
                                     const int* block_table, int tokens, int hq, int hkv, int d,
                                     int page_size, int num_pages, int max_pages, int slots,
-                                    int window, float scale, int* fault, cudaStream_t stream) {
+                                    int window, float scale, float softcap, const float* sink, int* fault,
+                                    cudaStream_t stream) {
   if (tokens == 0) return 0;
   if (d <= 0 || d % 16 != 0 || d > rl::kGenericMaxD || hkv <= 0 || hq % hkv != 0 ||
-      page_size <= 0 || window < 0)
+      page_size <= 0 || window < 0 || softcap < 0.0f)
     return static_cast<int>(cudaErrorInvalidValue);
   const long long items = static_cast<long long>(tokens) * hq;
   const unsigned blocks =
@@ -132,7 +141,7 @@ extern "C" int rl_attention_generic(int dtype, const void* q, const void* cache,
     rl::attention_generic_kernel<scalar_t><<<blocks, rl::kGenericWarps * 32, 0, stream>>>(
         static_cast<const scalar_t*>(q), static_cast<const scalar_t*>(cache),
         static_cast<scalar_t*>(out), positions, token_slot, block_table, tokens, hq, hkv, d,
-        page_size, num_pages, max_pages, slots, window, scale, fault);
+        page_size, num_pages, max_pages, slots, window, scale, softcap, sink, fault);
   });
   return rl::launch_status();
 }

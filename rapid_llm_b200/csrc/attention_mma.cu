@@ -66,6 +66,12 @@ struct AttentionArgs {
   int hq, hkv, page_size, num_pages, max_pages, slots, window, splits;
   float scale_log2;         // scale * log2(e)
   int* fault;
+  // Squashed scores and a sink (the mma.sync tiles and the merge kernel; the tcgen05 kernels take neither):
+  // with softcap > 0 a score s becomes softcap * tanh(s / softcap) after the scale; with `sink` ([hq], float32)
+  // every row's denominator also holds exp(sink[head]), a term without a key or a value, counted once.
+  float scale;              // the plain scale (used with softcap)
+  float softcap;            // 0 = scores are not squashed
+  const float* sink;        // null = no sink
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -332,7 +338,12 @@ attention_mma_kernel(const AttentionArgs args) {
           const int j = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
           const int i = e >> 1;
           const bool keep = j <= row_pos[i] && j >= row_lo[i] && j < k_end;
-          const float v = keep ? s[nt][e] * args.scale_log2 : -INFINITY;
+          float v = -INFINITY;
+          if (keep) {
+            v = args.softcap > 0.0f
+                    ? args.softcap * tanhf(s[nt][e] * args.scale / args.softcap) * 1.4426950408889634f
+                    : s[nt][e] * args.scale_log2;
+          }
           s[nt][e] = v;
           block_max[i] = fmaxf(block_max[i], v);
         }
@@ -397,8 +408,15 @@ attention_mma_kernel(const AttentionArgs args) {
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       if (!row_valid[i]) continue;
-      const float inv = run_sum[i] > 0.0f ? 1.0f / run_sum[i] : 0.0f;
+      float inv = run_sum[i] > 0.0f ? 1.0f / run_sum[i] : 0.0f;
       const size_t row = static_cast<size_t>(row_token[i]) * args.hq + row_head[i];
+      if (args.splits == 1 && args.sink != nullptr) {
+        // the sink joins the denominator of an unsplit row here (of a split one in the merge kernel)
+        const float sink2 = args.sink[row_head[i]] * 1.4426950408889634f;
+        const float top = fmaxf(run_max[i], sink2);
+        const float keys = run_max[i] == -INFINITY ? 0.0f : exp2f(run_max[i] - top);
+        inv = keys / (run_sum[i] * keys + exp2f(sink2 - top));
+      }
       if (args.splits == 1) {
         bf16* dst = args.out + row * kD + (lane & 3) * 2;
 #pragma unroll
@@ -451,10 +469,16 @@ attention_mma_kernel(const AttentionArgs args) {
         total += weight * merge_ml[(w * 16 + r) * 2 + 1];
         value += weight * merge_o[(w * 16 + r) * kMergeStride + c];
       }
-      const float inv = total > 0.0f ? 1.0f / total : 0.0f;
+      float inv = total > 0.0f ? 1.0f / total : 0.0f;
       const int token = p / group;
       const size_t row = static_cast<size_t>(tok_begin + token) * args.hq + kv_head * group +
                          (p - token * group);
+      if (args.splits == 1 && args.sink != nullptr) {
+        const float sink2 = args.sink[kv_head * group + (p - token * group)] * 1.4426950408889634f;
+        const float top = fmaxf(m, sink2);
+        const float keys = m == -INFINITY ? 0.0f : exp2f(m - top);
+        inv = keys / (total * keys + exp2f(sink2 - top));
+      }
       if (args.splits == 1) {
         args.out[row * kD + c] = __float2bfloat16_rn(value * inv);
       } else {
@@ -470,17 +494,18 @@ attention_mma_kernel(const AttentionArgs args) {
 // order; one warp per (token, head) row.
 __global__ void attention_merge_kernel(const float* __restrict__ part_out,
                                        const float* __restrict__ part_lse, bf16* __restrict__ out,
-                                       long long rows, int splits) {
+                                       long long rows, int splits, const float* __restrict__ sink, int hq) {
   pdl_trigger();
   pdl_wait();
   const long long row = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
   const float* lse = part_lse + row * splits;
-  float m = -INFINITY;
+  const float sink2 = sink ? sink[row % hq] * 1.4426950408889634f : -INFINITY;
+  float m = sink2;
   for (int s = 0; s < splits; ++s) m = fmaxf(m, lse[s]);
   const float safe = m == -INFINITY ? 0.0f : m;
-  float total = 0.0f;
+  float total = sink ? exp2f(sink2 - safe) : 0.0f;      // the sink counts once, whatever the number of parts
   for (int s = 0; s < splits; ++s) total += exp2f(lse[s] - safe);
   const float inv = total > 0.0f ? 1.0f / total : 0.0f;
   for (int c = lane; c < kD; c += 32) {
@@ -697,8 +722,14 @@ int rl_attention_mma(const void* q, const void* cache, void* out, float* part_ou
                      const int* entry_slot, const int* block_table, int tokens, int hq, int hkv,
                      int head_dim, int page_size, int num_pages, int max_pages, int slots,
                      int window, int splits, float scale, int* fault, int pdl, int decode_kernel, int decode_rows,
-                     int chunk_rows, int decode_splits, cudaStream_t stream) {
+                     int chunk_rows, int decode_splits, float softcap, const float* sink, cudaStream_t stream) {
   if (tokens == 0 || (n_chunk_items == 0 && n_decode_items == 0)) return 0;
+  const bool plain_scores = !(softcap > 0.0f) && sink == nullptr;
+  if (!plain_scores) {          // squashed scores and sinks run on the mma.sync tiles only
+    if (softcap < 0.0f || chunk_rows == attn::kPfRows || (decode_splits > 0 && decode_splits != splits))
+      return static_cast<int>(cudaErrorInvalidValue);
+    decode_kernel = 1;
+  }
   if (head_dim != attn::kD || hkv <= 0 || hq % hkv != 0 || page_size <= 0 || window < 0 ||
       splits < 1 || (splits > 1 && (part_out == nullptr || part_lse == nullptr)) ||
       hkv > 65535 || n_chunk_items > 65535 || n_decode_items > 65535)      // grid y dimensions
@@ -723,6 +754,7 @@ int rl_attention_mma(const void* q, const void* cache, void* out, float* part_ou
   args.max_pages = max_pages; args.slots = slots; args.window = window; args.splits = splits;
   args.scale_log2 = scale * 1.4426950408889634f;
   args.fault = fault;
+  args.scale = scale; args.softcap = softcap; args.sink = sink;
   int status = 0;
   bool merged_in_cluster = false;
   if (n_chunk_items > 0) {
@@ -756,7 +788,7 @@ int rl_attention_mma(const void* q, const void* cache, void* out, float* part_ou
   if (splits > 1 && !merged_in_cluster) {
     const long long rows = static_cast<long long>(tokens) * hq;
     status = rl::launch_kernel(attn::attention_merge_kernel, dim3(static_cast<unsigned>((rows + 3) / 4)), dim3(128), 0,
-                               stream, pdl != 0, part_out, part_lse, static_cast<attn::bf16*>(out), rows, splits);
+                               stream, pdl != 0, part_out, part_lse, static_cast<attn::bf16*>(out), rows, splits, sink, hq);
   }
   return status;
 }
@@ -848,7 +880,7 @@ int rl_attention_mma_static_scratch(const void* q, const void* cache, void* out,
   }
   return rl_attention_mma(q, cache, out, part_out, part_lse, chunk_items, n_chunk_items, decode_items,
                           n_decode_items, cu_seqlens, entry_start, entry_slot, block_table, tokens, hq, hkv,
-                          head_dim, page_size, num_pages, max_pages, slots, window, splits, scale, fault, 0, 1, 0, 64, 0, stream);
+                          head_dim, page_size, num_pages, max_pages, slots, window, splits, scale, fault, 0, 1, 0, 64, 0, 0.0f, nullptr, stream);
 }
 
 }  // extern "C"

@@ -32,7 +32,8 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
 template <typename T>
 __global__ void embedding_kernel(T* __restrict__ out, const T* __restrict__ table,
                                  const int* __restrict__ ids, const int* __restrict__ feedback,
-                                 int feedback_rows, int hidden, int vocab, int* __restrict__ fault) {
+                                 int feedback_rows, int hidden, int vocab, int* __restrict__ fault,
+                                 float scale, float* __restrict__ stream) {
   pdl_trigger();
   const int row = blockIdx.x;
   int id = ids[row];
@@ -45,6 +46,16 @@ __global__ void embedding_kernel(T* __restrict__ out, const T* __restrict__ tabl
   T* dst = out + static_cast<size_t>(row) * hidden;
   constexpr int kVec = 16 / sizeof(T);
   pdl_wait();   // the output buffer may still be read by the previous step's kernels
+  if (scale != 1.0f || stream != nullptr) {
+    // a scaled embedding: the float32 product opens the residual stream, `out` is its rounding
+    float* sr = stream ? stream + static_cast<size_t>(row) * hidden : nullptr;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      const float v = to_float(src[i]) * scale;
+      if (sr) sr[i] = v;
+      dst[i] = from_float<T>(v);
+    }
+    return;
+  }
   if (hidden % kVec == 0) {
     const uint4* s = reinterpret_cast<const uint4*>(src);
     uint4* d = reinterpret_cast<uint4*>(dst);
@@ -60,6 +71,11 @@ __global__ void embedding_kernel(T* __restrict__ out, const T* __restrict__ tabl
 //   mode 0: r = x                 (first layer: the residual stream starts here)
 //   mode 1: r = x + residual
 //   mode 2: r = x, residual untouched and may be null (a plain norm)
+//   mode 3: r = residual, x unread (the norm of the stream itself, for models whose sublayers add
+//           their normed outputs to it)
+//   mode 4: the norm sits on a sublayer's output: y = x * rsqrt(mean(x^2) + eps) * weight joins the
+//           stream, residual += y (stored), and out = the new residual rounded to the engine's dtype,
+//           which is what the next sublayer reads
 // With `write_residual` the sum is stored back to `residual` (float32).
 // `extra_rows` (a row per token, the dtype of x) and `extra_vector` (float32, one row for all
 // tokens), where given, are added to r in that order before it is stored or normed: what a model
@@ -92,7 +108,7 @@ __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, float* __restrict__
     pdl_wait();
     float sum_sq = 0.0f;
     if (active) {
-      load8(xr + at, v);
+      if (mode == 3) load8(rr + at, v); else load8(xr + at, v);
       if (mode == 1) {
         float r[8];
         load8(rr + at, r);
@@ -111,7 +127,7 @@ __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, float* __restrict__
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] += extra[i];
       }
-      if (write_residual) store8(rr + at, v);
+      if (write_residual && mode != 4) store8(rr + at, v);
 #pragma unroll
       for (int i = 0; i < 8; ++i) sum_sq += v[i] * v[i];
     }
@@ -120,24 +136,37 @@ __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, float* __restrict__
     if (active) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[i] = v[i] * inv_rms * w[i];
+      if (mode == 4) {
+        float r[8];
+        load8(rr + at, r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] += r[i];
+        store8(rr + at, v);
+      }
       store8(o + at, v);
     }
   } else {
     pdl_wait();
     float sum_sq = 0.0f;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-      float v = to_float(xr[i]);
+      float v = mode == 3 ? rr[i] : to_float(xr[i]);
       if (mode == 1) v += rr[i];
       if (er) v += to_float(er[i]);
       if (extra_vector) v += extra_vector[i];
-      if (write_residual) rr[i] = v;
+      if (write_residual && mode != 4) rr[i] = v;
       row_values[i] = v;
       sum_sq += v * v;
     }
     sum_sq = block_sum(sum_sq, scratch);
     const float inv_rms = rsqrtf(sum_sq / static_cast<float>(hidden) + eps);
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
-      o[i] = from_float<TOut>(row_values[i] * inv_rms * weight[i]);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      float v = row_values[i] * inv_rms * weight[i];
+      if (mode == 4) {
+        v += rr[i];
+        rr[i] = v;
+      }
+      o[i] = from_float<TOut>(v);
+    }
   }
 }
 
@@ -183,6 +212,25 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
   }
 }
 
+// ------------------------------------------------------- clamped gate * (up + 1)
+// gate_up as above; g = min(gate, limit), u = clamp(up, -limit, limit);
+// out = g * sigmoid(alpha * g) * (u + 1), in float32, rounded once.
+template <typename T>
+__global__ void clamped_glu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int inter,
+                                   float limit, float alpha) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t total = static_cast<size_t>(rows) * inter;
+  for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t r = idx / inter;
+    const size_t c = idx - r * inter;
+    const float g = fminf(to_float(gate_up[r * 2 * inter + c]), limit);
+    const float u = fminf(fmaxf(to_float(gate_up[r * 2 * inter + inter + c]), -limit), limit);
+    out[idx] = from_float<T>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+  }
+}
+
 // -------------------------------------------------------------- conversions
 template <typename TIn>
 __global__ void to_float_kernel(const TIn* __restrict__ in, float* __restrict__ out, size_t n) {
@@ -215,13 +263,14 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 extern "C" {
 
 int rl_embedding(int dtype, void* out, const void* table, const int* ids, const int* feedback,
-                 int feedback_rows, int rows, int hidden, int vocab, int* fault, int pdl, cudaStream_t stream) {
+                 int feedback_rows, int rows, int hidden, int vocab, int* fault, float scale, float* stream_out,
+                 int pdl, cudaStream_t stream) {
   if (rows == 0) return 0;
   RL_DISPATCH_DTYPE(dtype, {
     const int threads = hidden >= 2048 ? 256 : 128;
     return rl::launch_kernel(rl::embedding_kernel<scalar_t>, dim3(rows), dim3(threads), 0, stream, pdl != 0,
                              static_cast<scalar_t*>(out), static_cast<const scalar_t*>(table), ids, feedback,
-                             feedback_rows, hidden, vocab, fault);
+                             feedback_rows, hidden, vocab, fault, scale, stream_out);
   });
   return 0;
 }
@@ -232,7 +281,7 @@ int rl_add_rmsnorm(int dtype, const void* x, float* residual, const float* weigh
                    int write_residual, const void* extra_rows, const float* extra_vector, int pdl,
                    cudaStream_t stream) {
   if (rows == 0) return 0;
-  if (mode < 0 || mode > 2 || (mode == 1 && residual == nullptr) ||
+  if (mode < 0 || mode > 4 || ((mode == 1 || mode >= 3) && residual == nullptr) ||
       (write_residual && residual == nullptr) || hidden <= 0)
     return static_cast<int>(cudaErrorInvalidValue);
   const bool vector = hidden % 8 == 0 && hidden <= 8 * 1024 && rl::aligned16(x) && rl::aligned16(out) &&
@@ -276,6 +325,20 @@ int rl_silu_mul(int dtype, const void* gate_up, void* out, int rows, int inter, 
     auto kernel = vector ? rl::silu_mul_kernel<scalar_t, true> : rl::silu_mul_kernel<scalar_t, false>;
     return rl::launch_kernel(kernel, dim3(static_cast<unsigned>(blocks)), dim3(threads), 0, stream, pdl != 0,
                              static_cast<const scalar_t*>(gate_up), static_cast<scalar_t*>(out), rows, inter);
+  });
+  return 0;
+}
+
+int rl_clamped_glu(int dtype, const void* gate_up, void* out, int rows, int inter, float limit, float alpha,
+                   int pdl, cudaStream_t stream) {
+  if (rows == 0 || inter == 0) return 0;
+  const size_t total = static_cast<size_t>(rows) * inter;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  RL_DISPATCH_DTYPE(dtype, {
+    return rl::launch_kernel(rl::clamped_glu_kernel<scalar_t>, dim3(static_cast<unsigned>(blocks)), dim3(256), 0,
+                             stream, pdl != 0, static_cast<const scalar_t*>(gate_up), static_cast<scalar_t*>(out),
+                             rows, inter, limit, alpha);
   });
   return 0;
 }

@@ -1,0 +1,438 @@
+// Routed feed-forward: router scores and top-k, grouping of the step's (token, expert) pairs by
+// expert, products over the groups, and the sum over a token's experts.
+//
+// A step's T tokens each choose `top` of E experts; pair i = t * top + j is token t's j-th choice.
+//   rl_router_topk    z = W_r h in float32 (W_r float32, h the engine's dtype), s = sigmoid(z), the
+//                     `top` largest s per token (ties: the lower index) with their s as weights; extra
+//                     rows of W_r behind the experts' give sigmoid gates per token (a shared expert's).
+//   rl_moe_plan       counts the pairs per expert and lays them out expert by expert in tiles of
+//                     kTileM rows: sorted[p] = i, tile tables, all on the device (no host round trip).
+//   rl_grouped_linear out rows = A rows @ W[e]^T over the tiles; A rows are fetched by token
+//                     (pair i reads row i / top) or by place p; with `gated`, W[e] is [2 F, K] (gate
+//                     rows, then up rows) and out = silu(w g) * (w u), w the pair's weight: the weight
+//                     scales the expert's input, and W (w h) = w (W h).
+//   rl_moe_combine    out[t] = sum_j y[t * top + j] (+ gate[t] * shared[t]), j in order, float32 sums.
+// A row's result does not depend on its tile's other rows or on the order in which the pairs of an
+// expert were laid out: the inner sums run over k in a fixed order per row.
+//
+// Two product kernels: float32 FMA tiles (the 32-bit engine; any sizes) and mma.sync m16n8k16 tiles
+// for bfloat16 (float32 accumulators).
+#include "common.cuh"
+
+namespace rl {
+
+constexpr int kMoeTileM = 32;     // pairs per tile
+constexpr int kMoeTileN = 64;     // output columns per block
+constexpr int kMoeTileK = 32;
+constexpr int kMoeThreads = 256;
+
+__device__ __forceinline__ float moe_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// ------------------------------------------------------------------ router
+// One warp per token.  scores live in shared memory ([warps][E + G]).
+template <typename T>
+__global__ void router_topk_kernel(const T* x, int x_stride, const float* __restrict__ w, int hidden, int experts,
+                                   int gates, int top, int* __restrict__ ids, float* __restrict__ weights,
+                                   float* __restrict__ gate_out, float* __restrict__ scores_out, int tokens) {
+  extern __shared__ float moe_scores[];
+  pdl_trigger();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  pdl_wait();
+  if (t >= tokens) return;
+  const int rows = experts + gates;
+  float* s = moe_scores + static_cast<size_t>(warp) * rows;
+  const T* xr = x + static_cast<size_t>(t) * x_stride;
+  for (int e = 0; e < rows; ++e) {
+    const float* wr = w + static_cast<size_t>(e) * hidden;
+    float acc = 0.0f;
+    for (int k = lane; k < hidden; k += 32) acc = fmaf(wr[k], to_float(xr[k]), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) s[e] = moe_sigmoid(acc);
+  }
+  __syncwarp();
+  if (scores_out)
+    for (int e = lane; e < experts; e += 32) scores_out[static_cast<size_t>(t) * experts + e] = s[e];
+  for (int g = lane; g < gates; g += 32) gate_out[static_cast<size_t>(t) * gates + g] = s[experts + g];
+  for (int j = 0; j < top; ++j) {
+    float best = -1.0f;
+    int best_e = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = s[e];
+      if (v > best) { best = v; best_e = e; }      // a lane's lowest index wins its ties
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+      const int other_e = __shfl_xor_sync(0xffffffffu, best_e, offset);
+      if (other > best || (other == best && other_e < best_e)) { best = other; best_e = other_e; }
+    }
+    if (lane == 0) {
+      ids[static_cast<size_t>(t) * top + j] = best_e;
+      weights[static_cast<size_t>(t) * top + j] = best;
+      s[best_e] = -2.0f;      // taken
+    }
+    __syncwarp();
+  }
+}
+
+// ------------------------------------------------------------------ plan
+// One block.  meta: [0] tiles, then per tile (expert, first place, rows).  `sorted` [pairs] receives pair
+// indices expert by expert.  `place_of` [pairs]: where pair i went (the inverse of sorted).
+__global__ void moe_plan_kernel(const int* __restrict__ ids, int pairs, int experts, int* __restrict__ sorted,
+                                int* __restrict__ place_of, int* __restrict__ meta, int max_tiles,
+                                int* __restrict__ fault) {
+  extern __shared__ int moe_counts[];      // [experts] counts, [experts] cursors
+  pdl_trigger();
+  int* counts = moe_counts;
+  int* cursor = moe_counts + experts;
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
+  pdl_wait();
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int e = ids[i];
+    if (e >= 0 && e < experts) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0, tiles = 0;
+    for (int e = 0; e < experts; ++e) {
+      cursor[e] = at;
+      for (int row = 0; row < counts[e]; row += kMoeTileM) {
+        if (tiles < max_tiles) {
+          meta[1 + 3 * tiles] = e;
+          meta[2 + 3 * tiles] = at + row;
+          meta[3 + 3 * tiles] = min(kMoeTileM, counts[e] - row);
+        }
+        ++tiles;
+      }
+      at += counts[e];
+    }
+    if (tiles > max_tiles) {
+      atomicOr(fault, kFaultSlot);
+      tiles = max_tiles;
+    }
+    meta[0] = tiles;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int e = ids[i];
+    if (e < 0 || e >= experts) continue;
+    const int p = atomicAdd(&cursor[e], 1);
+    sorted[p] = i;
+    place_of[i] = p;
+  }
+}
+
+// ------------------------------------------------------------------ products over the groups, float32 FMA
+// grid: (column blocks, max tiles).  A: rows of `a` (engine dtype) found by pair: by_token ? pair / top : place.
+// W: [experts, n_rows_w, K] with n_rows_w = gated ? 2 N : N.  out: gated ? act[place, N] (engine dtype)
+// : y[pair, N] (float32).
+template <typename T, bool kGated>
+__global__ void __launch_bounds__(kMoeThreads)
+grouped_linear_fma_kernel(const T* a, int a_stride, const T* __restrict__ w, const int* __restrict__ sorted,
+                          const int* __restrict__ meta, const float* __restrict__ pair_weight, int top, int by_token,
+                          int n, int k, T* out_act, float* out_y) {
+  __shared__ float sa[kMoeTileM][kMoeTileK + 1];
+  __shared__ float sw[kGated ? 2 : 1][kMoeTileN][kMoeTileK + 1];
+  __shared__ int s_pair[kMoeTileM];
+  pdl_trigger();
+  pdl_wait();
+  const int tile = blockIdx.y;
+  if (tile >= meta[0]) return;
+  const int expert = meta[1 + 3 * tile], place0 = meta[2 + 3 * tile], rows = meta[3 + 3 * tile];
+  const int n0 = blockIdx.x * kMoeTileN;
+  const int tid = threadIdx.x;
+  if (tid < kMoeTileM) s_pair[tid] = tid < rows ? sorted[place0 + tid] : -1;
+  __syncthreads();
+  const int tx = tid & 15, ty = tid >> 4;      // 16 x 16 threads: 4 columns x 2 rows each
+  float acc[kGated ? 2 : 1][2][4];
+#pragma unroll
+  for (int g = 0; g < (kGated ? 2 : 1); ++g)
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[g][r][c] = 0.0f;
+  const size_t w_rows = kGated ? 2 * static_cast<size_t>(n) : static_cast<size_t>(n);
+  const T* we = w + static_cast<size_t>(expert) * w_rows * k;
+  for (int k0 = 0; k0 < k; k0 += kMoeTileK) {
+    for (int idx = tid; idx < kMoeTileM * kMoeTileK; idx += kMoeThreads) {
+      const int r = idx / kMoeTileK, c = idx - r * kMoeTileK;
+      float v = 0.0f;
+      const int pair = s_pair[r];
+      if (pair >= 0 && k0 + c < k) {
+        const size_t row = by_token ? static_cast<size_t>(pair / top) : static_cast<size_t>(place0 + r);
+        v = to_float(a[row * a_stride + k0 + c]);
+      }
+      sa[r][c] = v;
+    }
+    for (int idx = tid; idx < kMoeTileN * kMoeTileK; idx += kMoeThreads) {
+      const int r = idx / kMoeTileK, c = idx - r * kMoeTileK;
+      const bool ok = n0 + r < n && k0 + c < k;
+      sw[0][r][c] = ok ? to_float(we[static_cast<size_t>(n0 + r) * k + k0 + c]) : 0.0f;
+      if constexpr (kGated) sw[1][r][c] = ok ? to_float(we[(static_cast<size_t>(n) + n0 + r) * k + k0 + c]) : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int kk = 0; kk < kMoeTileK; ++kk) {
+      const float a0 = sa[ty * 2][kk], a1 = sa[ty * 2 + 1][kk];
+#pragma unroll
+      for (int g = 0; g < (kGated ? 2 : 1); ++g) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const float wv = sw[g][tx * 4 + c][kk];
+          acc[g][0][c] = fmaf(a0, wv, acc[g][0][c]);
+          acc[g][1][c] = fmaf(a1, wv, acc[g][1][c]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = ty * 2 + r;
+    const int pair = s_pair[row];
+    if (pair < 0) continue;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int col = n0 + tx * 4 + c;
+      if (col >= n) continue;
+      if constexpr (kGated) {
+        const float scale = pair_weight ? pair_weight[pair] : 1.0f;
+        const float g = acc[0][r][c] * scale, u = acc[1][r][c] * scale;
+        out_act[static_cast<size_t>(place0 + row) * n + col] = from_float<T>(g / (1.0f + expf(-g)) * u);
+      } else {
+        out_y[static_cast<size_t>(pair) * n + col] = acc[0][r][c];
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ products over the groups, bfloat16 mma.sync
+// The same tiles on the tensor cores: 8 warps, warp (wm, wn) owns rows 16 wm .. and columns 16 wn .. of the
+// 32 x 64 tile (two m16n8 accumulators, twice that when gated).  Operands pass through shared memory in
+// chunks of 32 of k; float32 accumulators; k runs upward in steps of 16 per row, whatever the tile holds.
+__device__ __forceinline__ void moe_mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <bool kGated>
+__global__ void __launch_bounds__(kMoeThreads)
+grouped_linear_mma_kernel(const __nv_bfloat16* a, int a_stride, const __nv_bfloat16* __restrict__ w,
+                          const int* __restrict__ sorted, const int* __restrict__ meta,
+                          const float* __restrict__ pair_weight, int top, int by_token, int n, int k,
+                          __nv_bfloat16* out_act, float* out_y) {
+  constexpr int kStride = kMoeTileK + 8;      // elements; rows stay 16-byte aligned and spread over the banks
+  __shared__ __align__(16) __nv_bfloat16 sa[kMoeTileM][kStride];
+  __shared__ __align__(16) __nv_bfloat16 sw[kGated ? 2 : 1][kMoeTileN][kStride];
+  __shared__ int s_pair[kMoeTileM];
+  pdl_trigger();
+  pdl_wait();
+  const int tile = blockIdx.y;
+  if (tile >= meta[0]) return;
+  const int expert = meta[1 + 3 * tile], place0 = meta[2 + 3 * tile], rows = meta[3 + 3 * tile];
+  const int n0 = blockIdx.x * kMoeTileN;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid < kMoeTileM) s_pair[tid] = tid < rows ? sorted[place0 + tid] : -1;
+  __syncthreads();
+  const int wm = warp & 1, wn = warp >> 1;      // 2 x 4 warps: 16 rows x 16 columns each
+  float acc[kGated ? 2 : 1][2][4];
+#pragma unroll
+  for (int g = 0; g < (kGated ? 2 : 1); ++g)
+#pragma unroll
+    for (int t = 0; t < 2; ++t)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[g][t][c] = 0.0f;
+  const size_t w_rows = kGated ? 2 * static_cast<size_t>(n) : static_cast<size_t>(n);
+  const __nv_bfloat16* we = w + static_cast<size_t>(expert) * w_rows * k;
+  const bool wide = (k % 8 == 0) && (a_stride % 8 == 0) && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
+  const __nv_bfloat16 zero = __float2bfloat16_rn(0.0f);
+  for (int k0 = 0; k0 < k; k0 += kMoeTileK) {
+    if (wide) {
+      // 16-byte pieces: 4 per row of 32
+      for (int idx = tid; idx < kMoeTileM * 4; idx += kMoeThreads) {
+        const int r = idx >> 2, c = (idx & 3) * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        const int pair = s_pair[r];
+        if (pair >= 0 && k0 + c < k) {
+          const size_t row = by_token ? static_cast<size_t>(pair / top) : static_cast<size_t>(place0 + r);
+          v = *reinterpret_cast<const uint4*>(a + row * a_stride + k0 + c);
+        }
+        *reinterpret_cast<uint4*>(&sa[r][c]) = v;
+      }
+      for (int idx = tid; idx < kMoeTileN * 4; idx += kMoeThreads) {
+        const int r = idx >> 2, c = (idx & 3) * 8;
+        const bool ok = n0 + r < n && k0 + c < k;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (ok) v = *reinterpret_cast<const uint4*>(we + static_cast<size_t>(n0 + r) * k + k0 + c);
+        *reinterpret_cast<uint4*>(&sw[0][r][c]) = v;
+        if constexpr (kGated) {
+          uint4 u = make_uint4(0, 0, 0, 0);
+          if (ok) u = *reinterpret_cast<const uint4*>(we + (static_cast<size_t>(n) + n0 + r) * k + k0 + c);
+          *reinterpret_cast<uint4*>(&sw[1][r][c]) = u;
+        }
+      }
+    } else {
+      for (int idx = tid; idx < kMoeTileM * kMoeTileK; idx += kMoeThreads) {
+        const int r = idx / kMoeTileK, c = idx - r * kMoeTileK;
+        __nv_bfloat16 v = zero;
+        const int pair = s_pair[r];
+        if (pair >= 0 && k0 + c < k) {
+          const size_t row = by_token ? static_cast<size_t>(pair / top) : static_cast<size_t>(place0 + r);
+          v = a[row * a_stride + k0 + c];
+        }
+        sa[r][c] = v;
+      }
+      for (int idx = tid; idx < kMoeTileN * kMoeTileK; idx += kMoeThreads) {
+        const int r = idx / kMoeTileK, c = idx - r * kMoeTileK;
+        const bool ok = n0 + r < n && k0 + c < k;
+        sw[0][r][c] = ok ? we[static_cast<size_t>(n0 + r) * k + k0 + c] : zero;
+        if constexpr (kGated) sw[1][r][c] = ok ? we[(static_cast<size_t>(n) + n0 + r) * k + k0 + c] : zero;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < kMoeTileK; ks += 16) {
+      // A fragment (m16 x k16, row major): a0 (row g, k 2q..), a1 (row g + 8), a2 (row g, k + 8), a3 (row g + 8, k + 8)
+      const int gr = lane >> 2, q = (lane & 3) * 2;
+      uint32_t af[4];
+      af[0] = *reinterpret_cast<const uint32_t*>(&sa[wm * 16 + gr][ks + q]);
+      af[1] = *reinterpret_cast<const uint32_t*>(&sa[wm * 16 + gr + 8][ks + q]);
+      af[2] = *reinterpret_cast<const uint32_t*>(&sa[wm * 16 + gr][ks + q + 8]);
+      af[3] = *reinterpret_cast<const uint32_t*>(&sa[wm * 16 + gr + 8][ks + q + 8]);
+#pragma unroll
+      for (int g = 0; g < (kGated ? 2 : 1); ++g) {
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          // B fragment (k16 x n8, "col"): b0 (k 2q.., column gr), b1 (k + 8): W rows are the columns
+          const int col = wn * 16 + t * 8 + gr;
+          const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&sw[g][col][ks + q]);
+          const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&sw[g][col][ks + q + 8]);
+          moe_mma_bf16(acc[g][t], af, b0, b1);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  // C fragment: c0, c1: row gr, columns 2q, 2q + 1; c2, c3: row gr + 8
+  const int gr = lane >> 2, q = (lane & 3) * 2;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int row = wm * 16 + gr + 8 * half;
+    const int pair = s_pair[row];
+    if (pair < 0) continue;
+    const float scale = (kGated && pair_weight) ? pair_weight[pair] : 1.0f;
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int col = n0 + wn * 16 + t * 8 + q + c;
+        if (col >= n) continue;
+        if constexpr (kGated) {
+          const float g = acc[0][t][2 * half + c] * scale, u = acc[1][t][2 * half + c] * scale;
+          out_act[static_cast<size_t>(place0 + row) * n + col] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+        } else {
+          out_y[static_cast<size_t>(pair) * n + col] = acc[0][t][2 * half + c];
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ combine
+template <typename T>
+__global__ void moe_combine_kernel(const float* __restrict__ y, int top, const T* shared, const float* __restrict__ gate,
+                                   int gate_stride, T* __restrict__ out, int tokens, int hidden) {
+  pdl_trigger();
+  pdl_wait();
+  const long long total = static_cast<long long>(tokens) * hidden;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = idx / hidden;
+    const int c = static_cast<int>(idx - t * hidden);
+    float sum = 0.0f;
+    for (int j = 0; j < top; ++j) sum += y[(t * top + j) * hidden + c];
+    if (shared) sum += (gate ? gate[t * gate_stride] : 1.0f) * to_float(shared[idx]);
+    out[idx] = from_float<T>(sum);
+  }
+}
+
+}  // namespace rl
+
+extern "C" {
+
+int rl_moe_tile_rows() { return rl::kMoeTileM; }
+
+int rl_router_topk(int dtype, const void* x, int x_stride, const float* w, int hidden, int experts, int gates, int top,
+                   int* ids, float* weights, float* gate_out, float* scores_out, int tokens, int pdl,
+                   cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  if (experts < 1 || top < 1 || top > experts || gates < 0 || (gates > 0 && gate_out == nullptr) || hidden < 1)
+    return static_cast<int>(cudaErrorInvalidValue);
+  const int warps = 4;
+  const size_t smem = static_cast<size_t>(warps) * (experts + gates) * sizeof(float);
+  if (smem > 48 * 1024) return static_cast<int>(cudaErrorInvalidValue);
+  RL_DISPATCH_DTYPE(dtype, {
+    return rl::launch_kernel(rl::router_topk_kernel<scalar_t>, dim3((tokens + warps - 1) / warps), dim3(warps * 32),
+                             smem, stream, pdl != 0, static_cast<const scalar_t*>(x), x_stride, w, hidden, experts,
+                             gates, top, ids, weights, gate_out, scores_out, tokens);
+  });
+  return 0;
+}
+
+int rl_moe_plan(const int* ids, int pairs, int experts, int* sorted, int* place_of, int* meta, int max_tiles,
+                int* fault, int pdl, cudaStream_t stream) {
+  if (pairs == 0) return 0;
+  const size_t smem = 2 * static_cast<size_t>(experts) * sizeof(int);
+  if (experts < 1 || smem > 48 * 1024 || max_tiles < 1) return static_cast<int>(cudaErrorInvalidValue);
+  return rl::launch_kernel(rl::moe_plan_kernel, dim3(1), dim3(1024), smem, stream, pdl != 0, ids, pairs, experts,
+                           sorted, place_of, meta, max_tiles, fault);
+}
+
+// a: engine dtype rows; w: [experts, (gated ? 2 n : n), k] engine dtype; gated: out_act [pairs, n] engine dtype by
+// place; else out_y [pairs, n] float32 by pair.
+int rl_grouped_linear(int dtype, const void* a, int a_stride, const void* w, const int* sorted, const int* meta,
+                      const float* pair_weight, int top, int by_token, int n, int k, int gated, void* out_act,
+                      float* out_y, int max_tiles, int pdl, cudaStream_t stream) {
+  if (max_tiles == 0) return 0;
+  if (n < 1 || k < 1 || top < 1 || (gated && out_act == nullptr) || (!gated && out_y == nullptr) || max_tiles > 65535)
+    return static_cast<int>(cudaErrorInvalidValue);
+  const dim3 grid((n + rl::kMoeTileN - 1) / rl::kMoeTileN, max_tiles), block(rl::kMoeThreads);
+  if (dtype == rl::kBF16) {
+    using bf = __nv_bfloat16;
+    if (gated)
+      return rl::launch_kernel(rl::grouped_linear_mma_kernel<true>, grid, block, 0, stream, pdl != 0,
+                               static_cast<const bf*>(a), a_stride, static_cast<const bf*>(w), sorted, meta, pair_weight,
+                               top, by_token, n, k, static_cast<bf*>(out_act), out_y);
+    return rl::launch_kernel(rl::grouped_linear_mma_kernel<false>, grid, block, 0, stream, pdl != 0,
+                             static_cast<const bf*>(a), a_stride, static_cast<const bf*>(w), sorted, meta, pair_weight,
+                             top, by_token, n, k, static_cast<bf*>(out_act), out_y);
+  }
+  if (dtype != rl::kF32) return static_cast<int>(cudaErrorInvalidValue);
+  if (gated)
+    return rl::launch_kernel(rl::grouped_linear_fma_kernel<float, true>, grid, block, 0, stream, pdl != 0,
+                             static_cast<const float*>(a), a_stride, static_cast<const float*>(w), sorted, meta,
+                             pair_weight, top, by_token, n, k, static_cast<float*>(out_act), out_y);
+  return rl::launch_kernel(rl::grouped_linear_fma_kernel<float, false>, grid, block, 0, stream, pdl != 0,
+                           static_cast<const float*>(a), a_stride, static_cast<const float*>(w), sorted, meta,
+                           pair_weight, top, by_token, n, k, static_cast<float*>(out_act), out_y);
+}
+
+int rl_moe_combine(int dtype, const float* y, int top, const void* shared, const float* gate, int gate_stride,
+                   void* out, int tokens, int hidden, int pdl, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  const long long total = static_cast<long long>(tokens) * hidden;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  RL_DISPATCH_DTYPE(dtype, {
+    return rl::launch_kernel(rl::moe_combine_kernel<scalar_t>, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream,
+                             pdl != 0, y, top, static_cast<const scalar_t*>(shared), gate, gate_stride,
+                             static_cast<scalar_t*>(out), tokens, hidden);
+  });
+  return 0;
+}
+
+}  // extern "C"

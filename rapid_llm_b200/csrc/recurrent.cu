@@ -61,7 +61,8 @@ __global__ void causal_conv_silu_kernel(const T* x, int x_stride, int col0,
                                         const float* state, long long state_stride, int state_off,
                                         float* __restrict__ out, const int* __restrict__ cu_seqlens,
                                         const int* __restrict__ entry_slot, const int* __restrict__ entry_start,
-                                        int entries, int tokens, int C, int taps_given, int slots, int* __restrict__ fault) {
+                                        int entries, int tokens, int C, int taps_given, int slots, int* __restrict__ fault,
+                                        int act) {
   pdl_trigger();
   const int K = kTaps > 0 ? kTaps : taps_given;
   constexpr int kHeld = kTaps > 0 ? kTaps : kMaxTaps;
@@ -142,7 +143,7 @@ __global__ void causal_conv_silu_kernel(const T* x, int x_stride, int col0,
 #pragma unroll
       for (int d = 0; d < kHeld; ++d)
         if (d < K) acc[l] += w[l][K - 1 - d] * hist[l][d];
-      acc[l] = silu_f(acc[l]);
+      if (act) acc[l] = silu_f(acc[l]);      // act 0: the convolution's plain result
     }
     if constexpr (kLanes == 2) {
       *reinterpret_cast<float2*>(out + static_cast<size_t>(t) * C + c) = make_float2(acc[0], acc[1]);
@@ -187,6 +188,24 @@ __global__ void conv_tail_update_kernel(const T* x, int x_stride, int col0,
       fresh[j] = v;
     }
     for (int j = 0; j < K - 1; ++j) tail[static_cast<size_t>(j) * C + c] = fresh[j];
+  }
+}
+
+// ------------------------------------------------------------ activation into float32 rows
+// out[t, c] = act(x[t, col0 + c]) as float32 (act 0: the value itself, 1: SiLU): what a mixer without a
+// convolution feeds into its recurrence.
+template <typename T>
+__global__ void activate_rows_kernel(const T* x, int x_stride, int col0, float* __restrict__ out, int tokens, int C,
+                                     int act) {
+  pdl_trigger();
+  pdl_wait();
+  const long long total = static_cast<long long>(tokens) * C;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = idx / C;
+    const int c = static_cast<int>(idx - t * C);
+    const float v = to_float(x[static_cast<size_t>(t) * x_stride + col0 + c]);
+    out[idx] = act ? silu_f(v) : v;
   }
 }
 
@@ -806,9 +825,9 @@ extern "C" {
 int rl_causal_conv_silu(int dtype, const void* x, int x_stride, int col0, const float* taps, const float* bias,
                         float* state, long long state_stride, int state_off, float* out, const int* cu_seqlens,
                         const int* entry_slot, const int* entry_start, int entries, int tokens, int channels,
-                        int width, int slots, int* fault, int pdl, cudaStream_t stream) {
+                        int width, int slots, int* fault, int act, int pdl, cudaStream_t stream) {
   if (tokens == 0 || channels == 0) return 0;
-  if (width < 1 || width > rl::kMaxTaps || entries < 1) return static_cast<int>(cudaErrorInvalidValue);
+  if (width < 1 || width > rl::kMaxTaps || entries < 1 || act < 0 || act > 1) return static_cast<int>(cudaErrorInvalidValue);
   RL_DISPATCH_DTYPE(dtype, {
     const bool pairs = channels % 2 == 0 && col0 % 2 == 0 && x_stride % 2 == 0 &&
                        (reinterpret_cast<uintptr_t>(x) & 7) == 0 && (reinterpret_cast<uintptr_t>(out) & 7) == 0;
@@ -821,12 +840,24 @@ int rl_causal_conv_silu(int dtype, const void* x, int x_stride, int col0, const 
     int code = rl::launch_kernel(kernel, dim3(static_cast<unsigned>((threads + 127) / 128)), dim3(128), 0,
                                  stream, pdl != 0, static_cast<const scalar_t*>(x), x_stride, col0, taps, bias,
                                  static_cast<const float*>(state), state_stride, state_off, out, cu_seqlens,
-                                 entry_slot, entry_start, entries, tokens, channels, width, slots, fault);
+                                 entry_slot, entry_start, entries, tokens, channels, width, slots, fault, act);
     if (code != 0 || width == 1) return code;
     return rl::launch_kernel(rl::conv_tail_update_kernel<scalar_t>,
                              dim3(rl::flat_blocks(static_cast<long long>(entries) * channels, 256)), dim3(256), 0,
                              stream, pdl != 0, static_cast<const scalar_t*>(x), x_stride, col0, state, state_stride,
                              state_off, cu_seqlens, entry_slot, entry_start, entries, channels, width, slots);
+  });
+  return 0;
+}
+
+int rl_activate_rows(int dtype, const void* x, int x_stride, int col0, float* out, int tokens, int channels, int act,
+                     int pdl, cudaStream_t stream) {
+  if (tokens == 0 || channels == 0) return 0;
+  if (act < 0 || act > 1) return static_cast<int>(cudaErrorInvalidValue);
+  RL_DISPATCH_DTYPE(dtype, {
+    return rl::launch_kernel(rl::activate_rows_kernel<scalar_t>,
+                             dim3(rl::flat_blocks(static_cast<long long>(tokens) * channels, 256)), dim3(256), 0, stream,
+                             pdl != 0, static_cast<const scalar_t*>(x), x_stride, col0, out, tokens, channels, act);
   });
   return 0;
 }

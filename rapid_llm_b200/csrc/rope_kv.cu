@@ -389,3 +389,125 @@ extern "C" int rl_qk_norm_rope_write(int dtype, const void* qkv, int row_width, 
   });
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Rotation, then a weightless norm, then the cache write, from float32 rows: the order of a mixer
+// whose q, k and v come out of a short convolution (float32) and whose q and k are divided by their
+// root mean square AFTER the rotation.  The first `rotary` entries of a q or k head rotate (entry i
+// paired with i + rotary / 2, angle = position * inv_freq[i], float32 sincosf), the rest pass; the
+// head is then divided by sqrt(mean(x^2) + eps), the mean over its first `norm_size` entries (a
+// head's tail may be padding: zeros).  Values may be blended with the values an earlier layer left
+// for the same tokens, v <- (1 - mix) v + mix * first (mix: one float32 on the device), or left
+// there for later layers (first_mode 1: write, 2: read).  q goes to q_out, k and v into the pages,
+// all rounded once to the engine's dtype.  One warp per (token, head of q, k or v).
+namespace rl {
+
+struct RopeUnitArgs {
+  const float* in;          // [tokens, in_stride]: q heads, k heads, v heads, each of d entries
+  const float* inv_freq;    // [rotary / 2]
+  const int* positions;     // [tokens]
+  const int* kv_dest;       // [tokens] page * page_size + offset
+  const float* mix;         // one number, or null
+  float* first;             // [tokens, hkv * d] or null
+  void* q_out;              // [tokens, hq, d]
+  void* cache;              // [num_pages, 2, hkv, page_size, d]
+  int tokens, in_stride, hq, hkv, d, rotary, norm_size, page_size, num_pages, first_mode, unit;
+  float eps;
+  int* fault;
+};
+
+template <typename T>
+__global__ void rope_unit_write_kernel(const RopeUnitArgs a) {
+  pdl_trigger();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int per_token = a.hq + 2 * a.hkv;
+  const long long item = static_cast<long long>(blockIdx.x) * kRopeWarps + warp;
+  pdl_wait();
+  if (item >= static_cast<long long>(a.tokens) * per_token) return;
+  const int t = static_cast<int>(item / per_token);
+  const int head = static_cast<int>(item - static_cast<long long>(t) * per_token);
+  const float* src = a.in + static_cast<size_t>(t) * a.in_stride + static_cast<size_t>(head) * a.d;
+  const bool is_q = head < a.hq, is_v = head >= a.hq + a.hkv;
+  const int kv_head = is_q ? 0 : (is_v ? head - a.hq - a.hkv : head - a.hq);
+  constexpr int kPerLane = kMaxHeadDim / 32;
+  float x[kPerLane];
+  const int half = a.rotary >> 1;
+  const float pos = static_cast<float>(a.positions[t]);
+  float sum_sq = 0.0f;
+#pragma unroll
+  for (int j = 0; j < kPerLane; ++j) {
+    const int i = lane + 32 * j;
+    x[j] = 0.0f;
+    if (i >= a.d) continue;
+    float v = src[i];
+    if (!is_v && i < a.rotary) {
+      const int pair = i < half ? i : i - half;
+      float sn, cs;
+      sincosf(pos * a.inv_freq[pair], &sn, &cs);
+      const float other = src[i < half ? i + half : i - half];
+      v = i < half ? v * cs - other * sn : v * cs + other * sn;
+    }
+    x[j] = v;
+    if (i < a.norm_size) sum_sq += v * v;
+  }
+  if (!is_v && a.unit) {
+    sum_sq = warp_sum(sum_sq);
+    const float inv = rsqrtf(sum_sq / static_cast<float>(a.norm_size) + a.eps);
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j) x[j] *= inv;
+  }
+  T* dst;
+  if (is_q) {
+    dst = static_cast<T*>(a.q_out) + (static_cast<size_t>(t) * a.hq + head) * a.d;
+  } else {
+    const int dest = a.kv_dest[t];
+    const int page = dest / a.page_size, offset = dest - page * a.page_size;
+    if (dest < 0 || page >= a.num_pages) {
+      if (lane == 0) atomicOr(a.fault, kFaultPageId);
+      return;
+    }
+    dst = static_cast<T*>(a.cache) +
+          (((static_cast<size_t>(page) * 2 + (is_v ? 1 : 0)) * a.hkv + kv_head) * a.page_size + offset) * a.d;
+    if (is_v && a.first != nullptr) {
+      float* fr = a.first + (static_cast<size_t>(t) * a.hkv + kv_head) * a.d;
+      const float mix = a.first_mode == 2 && a.mix ? *a.mix : 0.0f;
+#pragma unroll
+      for (int j = 0; j < kPerLane; ++j) {
+        const int i = lane + 32 * j;
+        if (i >= a.d) continue;
+        if (a.first_mode == 1) fr[i] = x[j];
+        else if (a.first_mode == 2) x[j] = (1.0f - mix) * x[j] + mix * fr[i];
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kPerLane; ++j) {
+    const int i = lane + 32 * j;
+    if (i < a.d) dst[i] = from_float<T>(x[j]);
+  }
+}
+
+}  // namespace rl
+
+extern "C" int rl_rope_unit_write(int dtype, const float* in, int in_stride, const float* inv_freq,
+                                  const int* positions, const int* kv_dest, const float* mix, float* first,
+                                  int first_mode, void* q_out, void* cache, int tokens, int hq, int hkv, int d,
+                                  int rotary, int norm_size, int unit, float eps, int page_size, int num_pages,
+                                  int* fault, int pdl, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  if (d <= 0 || d > rl::kMaxHeadDim || rotary < 0 || rotary > d || (rotary & 1) || norm_size < 1 || norm_size > d ||
+      first_mode < 0 || first_mode > 2 || (first_mode != 0 && first == nullptr) || (first_mode == 2 && mix == nullptr) ||
+      page_size <= 0 || hq <= 0 || hkv <= 0 || (rotary > 0 && inv_freq == nullptr))
+    return static_cast<int>(cudaErrorInvalidValue);
+  rl::RopeUnitArgs a;
+  a.in = in; a.inv_freq = inv_freq; a.positions = positions; a.kv_dest = kv_dest; a.mix = mix; a.first = first;
+  a.q_out = q_out; a.cache = cache; a.tokens = tokens; a.in_stride = in_stride; a.hq = hq; a.hkv = hkv; a.d = d;
+  a.rotary = rotary; a.norm_size = norm_size; a.page_size = page_size; a.num_pages = num_pages;
+  a.first_mode = first_mode; a.unit = unit; a.eps = eps; a.fault = fault;
+  const long long warps = static_cast<long long>(tokens) * (hq + 2 * hkv);
+  const dim3 grid(static_cast<unsigned>((warps + rl::kRopeWarps - 1) / rl::kRopeWarps)), block(rl::kRopeWarps * 32);
+  RL_DISPATCH_DTYPE(dtype, {
+    return rl::launch_kernel(rl::rope_unit_write_kernel<scalar_t>, grid, block, 0, stream, pdl != 0, a);
+  });
+  return 0;
+}

@@ -114,8 +114,12 @@ class CausalLM:
     def forward(self, batch: StepBatch, caches: list[LayerCache]) -> torch.Tensor:
         """Logits ``[R, vocab]`` at ``batch.logit_rows``; runs only the tokens of the step."""
         batch.defer_products = True      # the queue is run below, before anything but a kernel reads a result
-        x = embedded = self.embedding.forward(batch)
-        residual = None
+        if getattr(self.embedding, "opens_stream", False):
+            x, residual = self.embedding.forward_stream(batch)      # the float32 stream starts at the embedding
+            embedded = x
+        else:
+            x = embedded = self.embedding.forward(batch)
+            residual = None
         schedule = self.spec.schedule
         for position, entry in enumerate(schedule):
             # the norm that the next layer starts with may ride on this layer's last product, unless
@@ -134,7 +138,9 @@ class CausalLM:
             gemm.flush()
         if batch.num_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=self.dtype, device=self.device)
-        if residual is None:
+        if residual is not None and self.layers[schedule[-1].layer].stream_in_residual:
+            hidden = self.final_norm.of_stream(residual, batch, row_index=batch.logit_rows, name="final_normed")
+        elif residual is None:
             hidden = self.final_norm.forward(
                 x, None, batch, mode=PLAIN, write_residual=False,
                 row_index=batch.logit_rows, name="final_normed",

@@ -116,9 +116,14 @@ def core() -> ctypes.CDLL:
     global _SIGNATURES_SET
     lib = load_library("core")
     if not _SIGNATURES_SET:
-        lib.rl_embedding.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
+        lib.rl_embedding.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_int, c_void_p]
         lib.rl_add_rmsnorm.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]
         lib.rl_silu_mul.argtypes = [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.rl_clamped_glu.argtypes = [c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p]
+        lib.rl_rope_unit_write.argtypes = [
+            c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int, c_void_p,
+        ]
         lib.rl_scatter_rows.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
         lib.rl_to_float.argtypes = [c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p]
         lib.rl_qk_norm_rope_write.argtypes = [
@@ -128,7 +133,7 @@ def core() -> ctypes.CDLL:
         ]
         lib.rl_attention_generic.argtypes = [
             c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
+            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_void_p,
         ]
         lib.rl_gemm_f32.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
         lib.rl_sample.argtypes = [
@@ -136,7 +141,8 @@ def core() -> ctypes.CDLL:
             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
         ]
         for name in (
-            "rl_embedding", "rl_scatter_rows", "rl_add_rmsnorm", "rl_silu_mul", "rl_to_float",
+            "rl_embedding", "rl_scatter_rows", "rl_add_rmsnorm", "rl_silu_mul", "rl_to_float", "rl_clamped_glu",
+            "rl_rope_unit_write",
             "rl_qk_norm_rope_write", "rl_attention_generic", "rl_gemm_f32", "rl_sample",
         ):
             getattr(lib, name).restype = c_int
@@ -146,11 +152,15 @@ def core() -> ctypes.CDLL:
 
 # --------------------------------------------------------------------------- ops
 def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, fault: torch.Tensor,
-              feedback: torch.Tensor | None = None) -> torch.Tensor:
-    """``out[t] = table[ids[t]]``; ``ids`` int32 ``[T]``; bad ids set the fault word.
+              feedback: torch.Tensor | None = None, scale: float = 1.0, stream: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[t] = table[ids[t]] * scale``; ``ids`` int32 ``[T]``; bad ids set the fault word.
 
-    With ``feedback`` (int32, on the device) an id ``-(r + 1)`` is replaced by ``feedback[r]``."""
-    _need_cuda(out, table, ids, fault, feedback)
+    With ``feedback`` (int32, on the device) an id ``-(r + 1)`` is replaced by ``feedback[r]``.  ``stream``
+    (float32 ``[T, H]``) also receives the rows, as the float32 products before ``out``'s rounding."""
+    _need_cuda(out, table, ids, fault, feedback, stream)
+    _expect("stream", stream, torch.float32), _contig("stream", stream)
+    if stream is not None and stream.shape != out.shape:
+        raise KernelError("embedding: stream must have the shape of out")
     _expect("ids", ids, torch.int32), _expect("feedback", feedback, torch.int32)
     _contig("out", out), _contig("table", table), _contig("ids", ids)
     if out.dtype != table.dtype or out.shape != (ids.numel(), table.shape[1]):
@@ -158,7 +168,7 @@ def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, fault: 
     _check(
         core().rl_embedding(dtype_tag(table.dtype), _ptr(out), _ptr(table), _ptr(ids), _ptr(feedback),
                             0 if feedback is None else feedback.numel(), ids.numel(),
-                            table.shape[1], table.shape[0], _ptr(fault), 0, _stream()),   # first kernel of a step: an ordinary launch
+                            table.shape[1], table.shape[0], _ptr(fault), float(scale), _ptr(stream), 0, _stream()),   # first kernel of a step: an ordinary launch
         "embedding",
     )
     return out
@@ -222,6 +232,75 @@ def add_rmsnorm(
         f"add_rmsnorm(hidden={hidden})",
     )
     return out
+
+
+def stream_rmsnorm(residual: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
+                   row_index: torch.Tensor | None = None) -> torch.Tensor:
+    """RMSNorm of the float32 stream itself (rows picked by ``row_index``), into ``out`` of the engine's dtype."""
+    _need_cuda(residual, weight, out, row_index)
+    _expect("weight", weight, torch.float32), _expect("residual", residual, torch.float32)
+    _expect("row_index", row_index, torch.int32), _contig("residual", residual), _contig("out", out)
+    hidden = residual.shape[-1]
+    rows = row_index.numel() if row_index is not None else residual.shape[0]
+    if weight.numel() != hidden or out.shape != (rows, hidden):
+        raise KernelError("stream_rmsnorm: shapes of residual, weight and out do not agree")
+    _check(core().rl_add_rmsnorm(dtype_tag(out.dtype), None, _ptr(residual), _ptr(weight), _ptr(out), _ptr(row_index),
+                                 rows, hidden, float(eps), 3, 0, None, None, int(PDL), _stream()), "stream_rmsnorm")
+    return out
+
+
+def join_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float) -> torch.Tensor:
+    """A norm on a sublayer's output: ``residual += x * rsqrt(mean(x^2) + eps) * weight`` (float32, in place) and
+    ``out`` = the new residual in the engine's dtype."""
+    _need_cuda(x, residual, weight, out)
+    _expect("weight", weight, torch.float32), _expect("residual", residual, torch.float32)
+    _contig("x", x), _contig("residual", residual), _contig("out", out)
+    if residual.shape != x.shape or out.shape != x.shape or out.dtype != x.dtype or weight.numel() != x.shape[-1]:
+        raise KernelError("join_rmsnorm: shapes of x, residual, weight and out do not agree")
+    _check(core().rl_add_rmsnorm(dtype_tag(x.dtype), _ptr(x), _ptr(residual), _ptr(weight), _ptr(out), None,
+                                 x.shape[0], x.shape[1], float(eps), 4, 1, None, None, int(PDL), _stream()), "join_rmsnorm")
+    return out
+
+
+def clamped_glu(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
+    """``out = g * sigmoid(alpha g) * (u + 1)`` with ``g = min(gate_up[:, :I], limit)``, ``u = clamp(gate_up[:, I:], +-limit)``."""
+    _need_cuda(gate_up, out)
+    _contig("gate_up", gate_up), _contig("out", out)
+    rows, width = gate_up.shape
+    if width % 2 or out.shape != (rows, width // 2) or out.dtype != gate_up.dtype:
+        raise KernelError("clamped_glu: out must be [rows, width / 2] of the input's dtype")
+    _check(core().rl_clamped_glu(dtype_tag(gate_up.dtype), _ptr(gate_up), _ptr(out), rows, width // 2, float(limit),
+                                 float(alpha), int(PDL), _stream()), "clamped_glu")
+    return out
+
+
+def rope_unit_write(rows: torch.Tensor, q_out: torch.Tensor, *, num_heads: int, num_kv_heads: int, head_dim: int,
+                    inv_freq: torch.Tensor | None, positions: torch.Tensor, kv_dest: torch.Tensor, cache: torch.Tensor,
+                    page_size: int, norm_size: int, unit: bool, eps: float, fault: torch.Tensor,
+                    first: torch.Tensor | None = None, first_mode: int = 0, mix: torch.Tensor | None = None) -> torch.Tensor:
+    """From float32 ``rows [T, (Hq + 2 Hkv) D]`` (a convolution's results): the first ``2 len(inv_freq)`` entries of
+    every q and k head rotate by position, the heads are then divided by their root mean square over the first
+    ``norm_size`` entries (``unit``), q goes to ``q_out`` and k, v into the pages.  ``first`` (float32
+    ``[T, Hkv D]``): with ``first_mode`` 1 the values are left there, with 2 they are blended with what lies
+    there, ``v <- (1 - mix) v + mix first`` (``mix``: one float32 on the device), before they are cached."""
+    _need_cuda(rows, q_out, inv_freq, positions, kv_dest, cache, fault, first, mix)
+    _expect("rows", rows, torch.float32), _expect("inv_freq", inv_freq, torch.float32), _expect("first", first, torch.float32)
+    _expect("mix", mix, torch.float32), _expect("positions", positions, torch.int32), _expect("kv_dest", kv_dest, torch.int32)
+    _contig("rows", rows), _contig("q_out", q_out), _contig("cache", cache), _contig("first", first)
+    tokens = rows.shape[0]
+    if rows.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim or q_out.numel() != tokens * num_heads * head_dim:
+        raise KernelError("rope_unit_write: rows or q_out do not fit the heads")
+    if cache.dtype != q_out.dtype or cache.shape[1:] != (2, num_kv_heads, page_size, head_dim):
+        raise KernelError("rope_unit_write: cache must be [pages, 2, kv_heads, page_size, head_dim] of q_out's dtype")
+    if first is not None and first.shape != (tokens, num_kv_heads * head_dim):
+        raise KernelError("rope_unit_write: first must be [tokens, kv_heads * head_dim]")
+    rotary = 0 if inv_freq is None else 2 * inv_freq.numel()
+    _check(core().rl_rope_unit_write(
+        dtype_tag(q_out.dtype), _ptr(rows), rows.stride(0), _ptr(inv_freq), _ptr(positions), _ptr(kv_dest), _ptr(mix),
+        _ptr(first), int(first_mode), _ptr(q_out), _ptr(cache), tokens, num_heads, num_kv_heads, head_dim, rotary,
+        int(norm_size), int(unit), float(eps), page_size, cache.shape[0], _ptr(fault), int(PDL), _stream()),
+        f"rope_unit_write(head_dim={head_dim})")
+    return q_out
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -319,9 +398,16 @@ def attention_generic(
     window: int,
     scale: float,
     fault: torch.Tensor,
+    softcap: float = 0.0,
+    sink: torch.Tensor | None = None,
 ) -> torch.Tensor:
-    """Causal attention of every token of the step over its request's cached keys."""
-    _need_cuda(q, cache, out, positions, token_slot, block_table, fault)
+    """Causal attention of every token of the step over its request's cached keys.  ``softcap`` > 0 squashes the
+    scaled scores to ``softcap * tanh(s / softcap)``; ``sink`` (float32 ``[heads]``) adds ``exp(sink[h])`` to every
+    row's denominator."""
+    _need_cuda(q, cache, out, positions, token_slot, block_table, fault, sink)
+    _expect("sink", sink, torch.float32), _contig("sink", sink)
+    if sink is not None and sink.numel() != num_heads:
+        raise KernelError("attention: one sink per head")
     _contig("q", q), _contig("cache", cache), _contig("out", out), _contig("block_table", block_table)
     for name, tensor in (("positions", positions), ("token_slot", token_slot), ("block_table", block_table)):
         _expect(name, tensor, torch.int32)
@@ -339,7 +425,7 @@ def attention_generic(
             dtype_tag(q.dtype), _ptr(q), _ptr(cache), _ptr(out), _ptr(positions), _ptr(token_slot),
             _ptr(block_table), tokens, num_heads, num_kv_heads, head_dim, cache.shape[3],
             cache.shape[0], block_table.shape[1], block_table.shape[0], int(window), float(scale),
-            _ptr(fault), _stream(),
+            float(softcap), _ptr(sink), _ptr(fault), _stream(),
         ),
         f"attention_generic(head_dim={head_dim})",
     )
@@ -370,7 +456,7 @@ def attention_lib(head_dim: int) -> ctypes.CDLL:
         lib.rl_attention_mma.argtypes = [
             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-            c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+            c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
         ]
         lib.rl_attention_mma.restype = c_int
         lib.rl_attention_decode_max_clusters.argtypes = [c_int]
@@ -425,6 +511,8 @@ def attention_mma(
     decode_rows: int = 0,
     chunk_rows: int = CHUNK_TILE_ROWS,
     decode_splits: int = 0,
+    softcap: float = 0.0,
+    sink: torch.Tensor | None = None,
 ) -> torch.Tensor:
     """bfloat16 paged causal attention over work items the host cut the step into.
 
@@ -441,9 +529,16 @@ def attention_mma(
     D]`` / ``part_lse`` ``[T * Hq * splits]`` (float32) are scratch.  ``decode_splits`` (0 = as ``splits``) gives
     the decode items a split count of their own, merged inside the tcgen05 decode kernel's clusters: only with
     ``splits == 1``, where that kernel applies, up to 16.
+
+    ``softcap`` > 0 squashes the scaled scores to ``softcap * tanh(s / softcap)``; ``sink`` (float32 ``[heads]``)
+    adds ``exp(sink[h])`` to every row's denominator, once.  Either one keeps the step on the mma.sync tiles
+    (``chunk_rows`` must then be :data:`CHUNK_TILE_ROWS`).
     """
     _need_cuda(q, cache, out, chunk_items, decode_items, part_out, part_lse, cu_seqlens, entry_start,
-               entry_slot, block_table, fault)
+               entry_slot, block_table, fault, sink)
+    _expect("sink", sink, torch.float32), _contig("sink", sink)
+    if sink is not None and sink.numel() != num_heads:
+        raise KernelError("attention: one sink per head")
     for name, tensor in (("q", q), ("cache", cache), ("out", out)):
         _expect(name, tensor, torch.bfloat16), _contig(name, tensor)
     for name, tensor in (("chunk_items", chunk_items), ("decode_items", decode_items), ("cu_seqlens", cu_seqlens),
@@ -471,7 +566,7 @@ def attention_mma(
             _ptr(block_table), tokens, num_heads, num_kv_heads, head_dim, cache.shape[3], cache.shape[0],
             block_table.shape[1], block_table.shape[0], int(window), int(splits), float(scale),
             _ptr(fault), int(PDL), {"auto": 0, "mma": 1, "deep": 2, "shallow": 3}[decode_kernel], int(decode_rows), int(chunk_rows),
-            int(decode_splits), _stream(),
+            int(decode_splits), float(softcap), _ptr(sink), _stream(),
         ),
         f"attention_mma(head_dim={head_dim})",
     )
@@ -814,8 +909,9 @@ def recurrent() -> ctypes.CDLL:
     if not _RECURRENT_SET:
         lib.rl_causal_conv_silu.argtypes = [
             c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p,
-            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
+            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
         ]
+        lib.rl_activate_rows.argtypes = [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
         lib.rl_decay_gate.argtypes = [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                       c_int, c_int, c_int, c_void_p]
         lib.rl_unit_heads.argtypes = [c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_float,
@@ -831,7 +927,7 @@ def recurrent() -> ctypes.CDLL:
                                       c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
         lib.rl_xielu.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p]
         lib.rl_scaled_sum.argtypes = [c_int, c_void_p, c_void_p, c_float, c_float, c_void_p, c_longlong, c_int, c_void_p]
-        for name in ("rl_causal_conv_silu", "rl_decay_gate", "rl_unit_heads", "rl_rotate_heads", "rl_linear_scan",
+        for name in ("rl_causal_conv_silu", "rl_activate_rows", "rl_decay_gate", "rl_unit_heads", "rl_rotate_heads", "rl_linear_scan",
                      "rl_gated_norm", "rl_xielu", "rl_scaled_sum"):
             getattr(lib, name).restype = c_int
         _RECURRENT_SET = True
@@ -852,8 +948,9 @@ def _state_row(state: torch.Tensor) -> tuple[int, int]:
 
 
 def causal_conv_silu(x: torch.Tensor, taps: torch.Tensor, bias: torch.Tensor | None, tail: torch.Tensor,
-                     out: torch.Tensor, batch) -> torch.Tensor:
-    """``out[t, c] = silu(bias[c] + sum_d taps[c, K - 1 - d] * x[t - d, c])`` over each request's own tokens.
+                     out: torch.Tensor, batch, act: bool = True) -> torch.Tensor:
+    """``out[t, c] = silu(bias[c] + sum_d taps[c, K - 1 - d] * x[t - d, c])`` over each request's own tokens
+    (without the SiLU when ``act`` is false).
 
     ``x`` is ``[T, C]`` (a view of columns of the step's rows), ``taps`` float32 ``[C, K]`` with the current
     token's tap last, ``tail`` float32 ``[slots, (K - 1) * C]``: every slot's last ``K - 1`` inputs, oldest
@@ -871,9 +968,20 @@ def causal_conv_silu(x: torch.Tensor, taps: torch.Tensor, bias: torch.Tensor | N
         recurrent().rl_causal_conv_silu(
             dtype_tag(x.dtype), _ptr(x), _row_stride("x", x), 0, _ptr(taps), _ptr(bias), _ptr(tail), stride, 0,
             _ptr(out), _ptr(batch.cu_seqlens), _ptr(batch.entry_slot), _ptr(batch.entry_start), batch.num_entries,
-            tokens, channels, width, slots, _ptr(batch.fault), int(PDL), _stream()),
+            tokens, channels, width, slots, _ptr(batch.fault), int(bool(act)), int(PDL), _stream()),
         f"causal_conv_silu(width={width})",
     )
+    return out
+
+
+def activate_rows(x: torch.Tensor, out: torch.Tensor, act: bool = True) -> torch.Tensor:
+    """``out = silu(x)`` (or ``x`` itself) as float32; ``x [T, C]`` may be a view of columns."""
+    _need_cuda(x, out)
+    _expect("out", out, torch.float32), _contig("out", out)
+    if out.shape != x.shape:
+        raise KernelError("activate_rows: out must have the shape of x")
+    _check(recurrent().rl_activate_rows(dtype_tag(x.dtype), _ptr(x), _row_stride("x", x), 0, _ptr(out), x.shape[0],
+                                        x.shape[1], int(bool(act)), int(PDL), _stream()), "activate_rows")
     return out
 
 
@@ -1024,6 +1132,101 @@ def scaled_sum(a: torch.Tensor, b: torch.Tensor, a_scale: float, b_scale: float,
         raise KernelError("scaled_sum: shapes do not agree")
     _check(recurrent().rl_scaled_sum(dtype_tag(a.dtype), _ptr(a), _ptr(b), float(a_scale), float(b_scale), _ptr(out),
                                      a.numel(), int(PDL), _stream()), "scaled_sum")
+    return out
+
+
+# ------------------------------------------------------------- routed feed-forward
+_MOE_LIB: ctypes.CDLL | None = None
+
+
+def moe_lib() -> ctypes.CDLL:
+    """The library of the routed feed-forward's kernels (``csrc/moe.cu``), built at first use."""
+    global _MOE_LIB
+    if _MOE_LIB is None:
+        lib = load_library("moe")
+        lib.rl_router_topk.argtypes = [c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                       c_void_p, c_void_p, c_int, c_int, c_void_p]
+        lib.rl_moe_plan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p]
+        lib.rl_grouped_linear.argtypes = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                          c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]
+        lib.rl_moe_combine.argtypes = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                                       c_void_p]
+        for name in ("rl_router_topk", "rl_moe_plan", "rl_grouped_linear", "rl_moe_combine", "rl_moe_tile_rows"):
+            getattr(lib, name).restype = c_int
+        _MOE_LIB = lib
+    return _MOE_LIB
+
+
+def moe_max_tiles(pairs: int, experts: int) -> int:
+    """Most tiles the (token, expert) pairs of a step can fall into."""
+    return -(-int(pairs) // int(moe_lib().rl_moe_tile_rows())) + int(experts)
+
+
+def router_topk(x: torch.Tensor, weight: torch.Tensor, *, experts: int, top: int, ids: torch.Tensor,
+                weights: torch.Tensor, gates: torch.Tensor | None = None, scores: torch.Tensor | None = None) -> None:
+    """``s = sigmoid(weight[:experts] @ x[t])`` in float32; ``ids[t]``/``weights[t]`` the ``top`` largest (ties: the
+    lower index) with their ``s``; rows of ``weight`` behind the experts' are gates, ``gates[t, g] = sigmoid(.)``."""
+    _need_cuda(x, weight, ids, weights, gates, scores)
+    _expect("weight", weight, torch.float32), _expect("ids", ids, torch.int32), _expect("weights", weights, torch.float32)
+    _expect("gates", gates, torch.float32), _expect("scores", scores, torch.float32)
+    _contig("weight", weight), _contig("ids", ids), _contig("weights", weights), _contig("gates", gates), _contig("scores", scores)
+    tokens, hidden = x.shape
+    extra = weight.shape[0] - experts
+    if weight.shape[1] != hidden or extra < 0 or ids.shape != (tokens, top) or weights.shape != (tokens, top) \
+            or (extra > 0 and (gates is None or gates.shape != (tokens, extra))):
+        raise KernelError("router_topk: shapes do not agree")
+    _check(moe_lib().rl_router_topk(dtype_tag(x.dtype), _ptr(x), _row_stride("x", x), _ptr(weight), hidden, experts, extra,
+                                    top, _ptr(ids), _ptr(weights), _ptr(gates), _ptr(scores), tokens, int(PDL), _stream()),
+           "router_topk")
+
+
+def moe_plan(ids: torch.Tensor, experts: int, sorted_pairs: torch.Tensor, place_of: torch.Tensor, meta: torch.Tensor,
+             fault: torch.Tensor) -> int:
+    """Groups the pairs ``ids [T, top]`` by expert on the device; returns the most tiles there can be."""
+    _need_cuda(ids, sorted_pairs, place_of, meta, fault)
+    for name, tensor in (("ids", ids), ("sorted_pairs", sorted_pairs), ("place_of", place_of), ("meta", meta)):
+        _expect(name, tensor, torch.int32), _contig(name, tensor)
+    pairs = ids.numel()
+    max_tiles = moe_max_tiles(pairs, experts)
+    if sorted_pairs.numel() < pairs or place_of.numel() < pairs or meta.numel() < 1 + 3 * max_tiles:
+        raise KernelError("moe_plan: the tables are too small")
+    _check(moe_lib().rl_moe_plan(_ptr(ids), pairs, experts, _ptr(sorted_pairs), _ptr(place_of), _ptr(meta), max_tiles,
+                                 _ptr(fault), int(PDL), _stream()), "moe_plan")
+    return max_tiles
+
+
+def grouped_linear(a: torch.Tensor, weight: torch.Tensor, sorted_pairs: torch.Tensor, meta: torch.Tensor, *, top: int,
+                   by_token: bool, max_tiles: int, pair_weight: torch.Tensor | None = None,
+                   out_act: torch.Tensor | None = None, out_y: torch.Tensor | None = None) -> None:
+    """Products over the pairs grouped by expert: ``weight [E, N or 2 N, K]``.  With ``out_act`` (engine dtype,
+    by place) the weight is gate rows then up rows and ``out_act = silu(w g) * (w u)`` with the pair's weight ``w``;
+    with ``out_y`` (float32, by pair) the plain product.  ``a`` rows are found by token (pair // top) or by place."""
+    _need_cuda(a, weight, sorted_pairs, meta, pair_weight, out_act, out_y)
+    _contig("weight", weight), _contig("out_act", out_act), _contig("out_y", out_y)
+    _expect("pair_weight", pair_weight, torch.float32), _expect("out_y", out_y, torch.float32)
+    gated = out_act is not None
+    if (out_y is None) == (out_act is None) or weight.dim() != 3 or weight.dtype != a.dtype or a.shape[1] != weight.shape[2]:
+        raise KernelError("grouped_linear: operands do not agree")
+    n = (out_act if gated else out_y).shape[1]
+    if weight.shape[1] != (2 * n if gated else n) or (gated and out_act.dtype != a.dtype):
+        raise KernelError("grouped_linear: the result's width does not fit the weight")
+    _check(moe_lib().rl_grouped_linear(dtype_tag(a.dtype), _ptr(a), _row_stride("a", a), _ptr(weight), _ptr(sorted_pairs),
+                                       _ptr(meta), _ptr(pair_weight), int(top), int(by_token), n, a.shape[1], int(gated),
+                                       _ptr(out_act), _ptr(out_y), int(max_tiles), int(PDL), _stream()), "grouped_linear")
+
+
+def moe_combine(y: torch.Tensor, top: int, out: torch.Tensor, shared: torch.Tensor | None = None,
+                gate: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[t] = sum_j y[t * top + j] (+ gate[t] * shared[t])``, float32 sums in the order of ``j``."""
+    _need_cuda(y, out, shared, gate)
+    _expect("y", y, torch.float32), _expect("gate", gate, torch.float32)
+    _contig("y", y), _contig("out", out), _contig("shared", shared)
+    tokens, hidden = out.shape
+    if y.shape != (tokens * top, hidden) or (shared is not None and (shared.shape != out.shape or shared.dtype != out.dtype)):
+        raise KernelError("moe_combine: shapes do not agree")
+    _check(moe_lib().rl_moe_combine(dtype_tag(out.dtype), _ptr(y), int(top), _ptr(shared), _ptr(gate),
+                                    0 if gate is None else _row_stride("gate", gate), _ptr(out), tokens, hidden, int(PDL),
+                                    _stream()), "moe_combine")
     return out
 
 

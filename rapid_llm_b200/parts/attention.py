@@ -30,7 +30,7 @@ import torch
 from ..config.model_spec import PartSpec
 from ..ops import gemm, kernels
 from .base import (
-    MATRIX, MIXERS, POSITION_ENCODINGS, VECTOR, CacheNeed, Mixer, StepPlanner, StepShape, TensorSpec,
+    MATRIX, MIXERS, POSITION_ENCODINGS, VECTOR, CacheNeed, Mixer, StateNeed, StepPlanner, StepShape, TensorSpec,
 )
 
 DEFAULT_SMS = 148         # a B200's; planning on the host without a device (tests) assumes it
@@ -80,14 +80,16 @@ class AttentionItems(StepPlanner):
     """
 
     def __init__(self, group: int, num_kv_heads: int, head_dim: int = 0, sms: int = DEFAULT_SMS,
-                 decode_clusters: dict[int, int] | None = None) -> None:
+                 decode_clusters: dict[int, int] | None = None, tensor_core: bool = True) -> None:
         self.group, self.num_kv_heads, self.head_dim = int(group), int(num_kv_heads), int(head_dim)
+        # False: the mixer's scores are squashed or its softmax has a sink, which only the mma.sync tiles compute
+        self.tensor_core = bool(tensor_core)
         self.decode_clusters = dict(decode_clusters or DEFAULT_DECODE_CLUSTERS)
         # work items the kernels want in flight: two CTAs per multiprocessor, one in a decode-only
         # step, whose kernel keeps a whole multiprocessor's shared memory busy
         self.target_ctas, self.decode_target_ctas = 2 * int(sms), int(sms)
         self.key = ("attention_items", self.group, self.num_kv_heads, self.head_dim, int(sms),
-                    tuple(sorted(self.decode_clusters.items())))
+                    tuple(sorted(self.decode_clusters.items())), self.tensor_core)
 
     def capacity(self, max_tokens: int, max_entries: int) -> int:
         chunk_tiles = -(-max_tokens * self.group // kernels.CHUNK_TILE_ROWS) + max_entries
@@ -99,7 +101,7 @@ class AttentionItems(StepPlanner):
         starts = np.asarray(shape.starts, dtype=np.int64)
         rows = lengths * self.group
         is_decode = (lengths == 1) | (rows <= kernels.DECODE_TILE_ROWS)
-        tensor_core = kernels.attention_tc_takes(self.head_dim, shape.page_size)
+        tensor_core = self.tensor_core and kernels.attention_tc_takes(self.head_dim, shape.page_size)
         for chunk_rows in ((kernels.CHUNK_TILE_ROWS_TC, kernels.CHUNK_TILE_ROWS) if tensor_core else (kernels.CHUNK_TILE_ROWS,)):
             tile_rows = np.where(is_decode, kernels.DECODE_TILE_ROWS, chunk_rows)
             tiles = -(-rows // tile_rows)
@@ -185,6 +187,11 @@ class GQAAttention(Mixer):
         value_dim: int | None = None,
         gate: str | None = None,
         names: dict[str, str] | None = None,
+        conv_width: int = 0,
+        unit_after_rotation: bool = False,
+        softcap: float = 0.0,
+        sink: bool = False,
+        value_mix: str | None = None,
         dtype,
         device,
     ) -> None:
@@ -202,9 +209,23 @@ class GQAAttention(Mixer):
         if (qkv_bias or shares_cache) and (padded != self.qk_dim or padded != self.v_dim):
             raise ValueError("padded head sizes are not combined with a bias or a shared cache")
         self.gate = gate
+        # Options of mixers whose q, k and v pass a short convolution: they take the float32 path between the
+        # projection and the cache (convolution, rotation, a weightless norm after it, blended values).
+        self.conv_width = int(conv_width)
+        self.unit_after_rotation = bool(unit_after_rotation)
+        self.softcap, self.has_sink = float(softcap), bool(sink)
+        if value_mix not in (None, "first", "later"):
+            raise ValueError(f"value_mix must be 'first', 'later' or None, got {value_mix!r}")
+        self.value_mix = value_mix
+        self.float_prelude = self.conv_width > 0 or self.unit_after_rotation or value_mix is not None
+        if self.float_prelude and (qk_norm or qkv_bias or shares_cache):
+            raise ValueError("the convolution path has no weighted q/k norm, bias or shared cache")
+        if not 0 <= self.conv_width <= 16 or self.softcap < 0:
+            raise ValueError("conv_width must lie between 0 and 16, softcap must not be negative")
         self.names = {name: name for name in (
             "q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight", "q_proj.bias", "k_proj.bias",
-            "v_proj.bias", "q_norm.weight", "k_norm.weight", "g_proj.weight")}
+            "v_proj.bias", "q_norm.weight", "k_norm.weight", "g_proj.weight", "q_conv", "k_conv", "v_conv", "sink",
+            "value_mix")}
         self.names.update(names or {})
         self.hidden = int(hidden_size)
         self.hq, self.hkv, self.d = int(num_heads), int(num_kv_heads), padded
@@ -217,7 +238,9 @@ class GQAAttention(Mixer):
         clusters = None
         if device.type == "cuda" and dtype == torch.bfloat16:
             clusters = kernels.attention_decode_clusters(self.d, device) or None
-        self._items = AttentionItems(self.hq // self.hkv, self.hkv, self.d, sms, clusters)
+        plain_scores = not self.softcap and not self.has_sink
+        self._items = AttentionItems(self.hq // self.hkv, self.hkv, self.d, sms, clusters if plain_scores else None,
+                                     tensor_core=plain_scores)
         self.position = POSITION_ENCODINGS.build(position, dtype=dtype, device=device)
         self.rotary_dim = int(position.params.get("rotary_dim", getattr(self.position, "rotary_dim", self.d)))
 
@@ -228,11 +251,25 @@ class GQAAttention(Mixer):
         self.q_norm = self.new_storage((self.d,), VECTOR) if self.qk_norm else None
         self.k_norm = self.new_storage((self.d,), VECTOR) if self.qk_norm and not self.shares_cache else None
         self.g = self.new_storage((self.hq * self.d, self.hidden), MATRIX) if self.gate else None
+        self.taps = self.new_storage((self.qkv.shape[0], self.conv_width), VECTOR) if self.conv_width > 0 else None
+        self.sink = self.new_storage((self.hq,), VECTOR) if self.has_sink else None
+        self.mix = self.new_storage((1,), VECTOR) if self.value_mix else None
+        self.inv_freq = None
+        if self.float_prelude and self.rotary_dim > 0:
+            if not hasattr(self.position, "inv_freq"):
+                raise ValueError("the convolution path computes its angles from frequencies: position kind 'rotary_frequencies'")
+            self.inv_freq = self.position.inv_freq
 
     # -- needs ----------------------------------------------------------------- #
     def cache_need(self) -> CacheNeed | None:
         kind = "window" if self.window > 0 else "full"
         return CacheNeed(kind, self.hkv, self.d, self.window)
+
+    def state_need(self) -> StateNeed | None:
+        """The convolution's last ``conv_width - 1`` inputs (projected q, k, v) per request, float32."""
+        if self.conv_width > 1:
+            return StateNeed(((self.conv_width - 1) * self.qkv.shape[0],), torch.float32)
+        return None
 
     def step_planner(self) -> StepPlanner | None:
         if self.dtype != torch.bfloat16:
@@ -257,6 +294,14 @@ class GQAAttention(Mixer):
                 specs["k_norm.weight"] = TensorSpec((self.qk_dim,), VECTOR, init="ones_normal")
         if self.gate:
             specs["g_proj.weight"] = TensorSpec((self.hq * self.v_dim, self.hidden))
+        if self.conv_width > 0:
+            specs["q_conv"] = TensorSpec((self.hq * self.qk_dim, self.conv_width), VECTOR)
+            specs["k_conv"] = TensorSpec((self.hkv * self.qk_dim, self.conv_width), VECTOR)
+            specs["v_conv"] = TensorSpec((self.hkv * self.v_dim, self.conv_width), VECTOR)
+        if self.has_sink:
+            specs["sink"] = TensorSpec((self.hq,), VECTOR)
+        if self.value_mix:
+            specs["value_mix"] = TensorSpec((), VECTOR)      # one number; the first such layer has it and does not use it
         return {self.names[name]: spec for name, spec in specs.items()}
 
     def _heads(self, rows: torch.Tensor, heads: int) -> torch.Tensor:
@@ -285,6 +330,18 @@ class GQAAttention(Mixer):
             self.qkv_bias[q_rows : q_rows + kv_rows].copy_(tensor.to(torch.float32))
         elif name == "v_proj.bias":
             self.qkv_bias[q_rows + kv_rows :].copy_(tensor.to(torch.float32))
+        elif name == "q_conv":
+            self._heads(self.taps[:q_rows], self.hq)[:, : self.qk_dim].copy_(tensor.to(torch.float32).view(self.hq, self.qk_dim, -1))
+        elif name == "k_conv":
+            self._heads(self.taps[q_rows : q_rows + kv_rows], self.hkv)[:, : self.qk_dim].copy_(
+                tensor.to(torch.float32).view(self.hkv, self.qk_dim, -1))
+        elif name == "v_conv":
+            self._heads(self.taps[q_rows + kv_rows :], self.hkv)[:, : self.v_dim].copy_(
+                tensor.to(torch.float32).view(self.hkv, self.v_dim, -1))
+        elif name == "sink":
+            self.sink.copy_(tensor.to(torch.float32))
+        elif name == "value_mix":
+            self.mix.copy_(tensor.to(torch.float32).reshape(1))
         elif name == "q_norm.weight":
             self.q_norm[: self.qk_dim].copy_(tensor.to(torch.float32))
         elif name == "k_norm.weight":
@@ -294,7 +351,7 @@ class GQAAttention(Mixer):
 
     def parameter_bytes(self) -> int:
         total = (self.qkv.numel() + self.o.numel() + (0 if self.g is None else self.g.numel())) * self.qkv.element_size()
-        for vector in (self.q_norm, self.k_norm, self.qkv_bias):
+        for vector in (self.q_norm, self.k_norm, self.qkv_bias, self.taps, self.sink, self.mix):
             if vector is not None:
                 total += vector.numel() * 4
         return total
@@ -304,7 +361,7 @@ class GQAAttention(Mixer):
         return self.qkv.shape[0] + 2 * self.hq * self.d + self.hidden + gate      # qkv, q, attended, projected
 
     def uses_libraries(self) -> set[str]:
-        found = {"recurrent"} if self.gate else set()
+        found = {"recurrent"} if self.gate or self.float_prelude else set()
         if self.dtype == torch.bfloat16:
             from ..ops.build import attention_library
             found |= {"gemm", attention_library(self.d)}
@@ -321,16 +378,10 @@ class GQAAttention(Mixer):
         qkv = batch.workspace.get("attn_qkv", rows, self.qkv.shape[0], x.dtype)
         gemm.linear(x, self.qkv, qkv, batch.fault, bias=self.qkv_bias, defer=batch.defer_products)
         q = batch.workspace.get("attn_q", rows, self.hq * self.d, x.dtype)
-        cos, sin = self.position.tables()
-        kernels.qk_norm_rope_write(
-            qkv, q,
-            num_heads=self.hq, num_kv_heads=self.hkv, head_dim=self.d, rotary_dim=self.rotary_dim,
-            cos=cos, sin=sin, positions=batch.positions, eps=self.eps, fault=batch.fault,
-            q_weight=self.q_norm, k_weight=self.k_norm,
-            kv_dest=group.kv_dest if cache.writes else None,
-            cache=cache.pages if cache.writes else None,
-            page_size=group.page_size, norm_size=self.qk_dim,
-        )
+        if self.float_prelude:
+            self._float_prelude(qkv, q, batch, cache, group)
+        else:
+            self._norm_rope_write(qkv, q, batch, cache, group)
         attended = batch.workspace.get("attn_out", rows, self.hq * self.d, x.dtype)
         self.attend(q, cache.pages, attended, batch, group)
         if self.gate:
@@ -341,6 +392,44 @@ class GQAAttention(Mixer):
                                           act=kernels.GATE_SIGMOID, norm=False)
         out = batch.workspace.get("attn_proj", rows, self.hidden, x.dtype)
         return gemm.linear(attended, self.o, out, batch.fault, then_norm=then_norm, defer=batch.defer_products)
+
+    def _float_prelude(self, qkv, q, batch, cache, group) -> None:
+        """Projection -> short convolution (float32, the slot's tail before the step's rows) -> rotation ->
+        weightless norm -> blended values -> q out, k and v into the pages."""
+        rows, width = qkv.shape
+        wide = batch.workspace.get("attn_conv", rows, width, torch.float32)
+        if self.conv_width > 0:
+            tail = cache.state
+            if self.conv_width > 1 and (tail is None or tail.shape[1] != (self.conv_width - 1) * width):
+                raise ValueError("the engine did not give this mixer the state row it asked for")
+            if tail is None:
+                tail = batch.workspace.get("attn_no_tail", 1, 0, torch.float32, min_rows=1)
+            kernels.causal_conv_silu(qkv, self.taps, None, tail, wide, batch, act=False)
+        else:
+            kernels.activate_rows(qkv, wide, act=False)
+        first, mode = None, 0
+        if self.value_mix:
+            # what the first blending layer's values were for this step's tokens: left there by it, read by the later ones
+            first = batch.workspace.get("attn_first_values", rows, self.hkv * self.d, torch.float32)
+            mode = 1 if self.value_mix == "first" else 2
+        kernels.rope_unit_write(
+            wide, q, num_heads=self.hq, num_kv_heads=self.hkv, head_dim=self.d, inv_freq=self.inv_freq,
+            positions=batch.positions, kv_dest=group.kv_dest, cache=cache.pages, page_size=group.page_size,
+            norm_size=self.qk_dim, unit=self.unit_after_rotation, eps=self.eps, fault=batch.fault,
+            first=first, first_mode=mode, mix=self.mix,
+        )
+
+    def _norm_rope_write(self, qkv, q, batch, cache, group) -> None:
+        cos, sin = self.position.tables()
+        kernels.qk_norm_rope_write(
+            qkv, q,
+            num_heads=self.hq, num_kv_heads=self.hkv, head_dim=self.d, rotary_dim=self.rotary_dim,
+            cos=cos, sin=sin, positions=batch.positions, eps=self.eps, fault=batch.fault,
+            q_weight=self.q_norm, k_weight=self.k_norm,
+            kv_dest=group.kv_dest if cache.writes else None,
+            cache=cache.pages if cache.writes else None,
+            page_size=group.page_size, norm_size=self.qk_dim,
+        )
 
     def attend(self, q, pages, out, batch, group) -> None:
         if q.dtype == torch.bfloat16:
@@ -359,12 +448,12 @@ class GQAAttention(Mixer):
                 block_table=group.block_table, num_heads=self.hq, num_kv_heads=self.hkv, head_dim=self.d,
                 window=self.window, scale=self.scale, fault=batch.fault, decode_rows=plan.get("decode_rows", 0),
                 chunk_rows=plan.get("chunk_rows", kernels.CHUNK_TILE_ROWS),
-                decode_splits=plan.get("decode_splits", 0),
+                decode_splits=plan.get("decode_splits", 0), softcap=self.softcap, sink=self.sink,
             )
             return
         kernels.attention_generic(
             q, pages, out,
             positions=batch.positions, token_slot=batch.token_slot, block_table=group.block_table,
             num_heads=self.hq, num_kv_heads=self.hkv, head_dim=self.d,
-            window=self.window, scale=self.scale, fault=batch.fault,
+            window=self.window, scale=self.scale, fault=batch.fault, softcap=self.softcap, sink=self.sink,
         )

@@ -242,6 +242,10 @@ class Block(Part):
     def step_planners(self) -> list[StepPlanner]:
         return []
 
+    # True for an arrangement that keeps the whole stream in ``residual`` (float32) and hands on, as ``x``, only its
+    # rounding to the engine's dtype: the model then norms ``residual`` alone at the end, not ``x + residual``.
+    stream_in_residual = False
+
     def leading_norm(self) -> "Norm | None":
         """The norm this block starts with, if the block takes its unscaled result
         (``ops.gemm.ScaledRows``) as ``x`` from the block before it."""

@@ -16,7 +16,7 @@ from __future__ import annotations
 import torch
 
 from ..config.model_spec import LayerSpec
-from ..ops import gemm
+from ..ops import gemm, kernels
 from ..ops.gemm import ScaledRows
 from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, TensorSpec
 from .norm import ADD, FIRST
@@ -129,3 +129,33 @@ class PreNormBlock(Block):
             offer = then_norm.following(residual, batch) if then_norm is not None else None
             return self.feed_forward.forward(normed, batch, then_norm=offer), residual
         return self.feed_forward.forward(normed, batch), residual
+
+
+@BLOCKS.register("outnorm")
+class OutputNormBlock(PreNormBlock):
+    """Norms on the sublayers' outputs: ``h <- h + Norm(Mixer(h)); h <- h + Norm(FeedForward(h))``.
+
+    The sublayers read the stream itself.  The stream lives in ``residual`` (float32) and every norm adds
+    its result there (one kernel: norm, add, store, and the sum's rounding to the engine's dtype, which is
+    what the next sublayer reads); ``x`` is that rounding.  No norm stands in front of a product, so none
+    rides on one."""
+
+    stream_in_residual = True
+
+    def leading_norm(self):
+        return None
+
+    def forward(self, x, residual, batch, cache, then_norm=None, addend=None):
+        if addend is not None or isinstance(x, ScaledRows):
+            raise ValueError("this arrangement takes plain rows and no addend")
+        if residual is None:       # the embedding did not open the stream: it starts as x
+            residual = batch.workspace.get("residual", x.shape[0], x.shape[1], torch.float32)
+            kernels.to_float(x, residual)
+        mixed = self.mixer.forward(x, batch, cache)
+        gemm.flush()
+        x = self.mixer_norm.join(mixed, residual, batch)
+        if self.feed_forward is not None:
+            wide = self.feed_forward.forward(x, batch)
+            gemm.flush()
+            x = self.feed_forward_norm.join(wide, residual, batch)
+        return x, residual

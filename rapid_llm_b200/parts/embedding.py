@@ -17,10 +17,16 @@ from .base import EMBEDDINGS, HEADS, MATRIX, VECTOR, Part, TensorSpec
 
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Part):
-    def __init__(self, *, vocab_size: int, hidden_size: int, dtype, device, name: str = "weight") -> None:
+    """``scale`` multiplies every row (float32 product).  With ``opens_stream`` the float32 products are also the
+    residual stream's first value (:meth:`forward_stream`), for models whose layers add to the stream without a
+    norm in front: the stream then never passes through the engine's 16-bit dtype."""
+
+    def __init__(self, *, vocab_size: int, hidden_size: int, dtype, device, name: str = "weight",
+                 scale: float = 1.0, opens_stream: bool = False) -> None:
         super().__init__(dtype=dtype, device=device)
         self.vocab, self.hidden = int(vocab_size), int(hidden_size)
         self.name = name          # the tensor's name after the part's prefix (may be empty)
+        self.scale, self.opens_stream = float(scale), bool(opens_stream)
         self.weight = self.new_storage((self.vocab, self.hidden), MATRIX)
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
@@ -36,7 +42,14 @@ class TokenEmbedding(Part):
 
     def forward(self, batch) -> torch.Tensor:
         out = batch.workspace.get("embedded", batch.num_tokens, self.hidden, self.dtype)
-        return kernels.embedding(out, self.weight, batch.token_ids, batch.fault, batch.feedback)
+        return kernels.embedding(out, self.weight, batch.token_ids, batch.fault, batch.feedback, scale=self.scale)
+
+    def forward_stream(self, batch) -> tuple[torch.Tensor, torch.Tensor]:
+        """``(rows in the engine's dtype, the float32 residual stream they open)``."""
+        out = batch.workspace.get("embedded", batch.num_tokens, self.hidden, self.dtype)
+        stream = batch.workspace.get("residual", batch.num_tokens, self.hidden, torch.float32)
+        kernels.embedding(out, self.weight, batch.token_ids, batch.fault, batch.feedback, scale=self.scale, stream=stream)
+        return out, stream
 
 
 @EMBEDDINGS.register("pass_offset")
@@ -66,9 +79,10 @@ class PassOffset(Part):
 
 @HEADS.register("lm_head")
 class LMHead(Part):
-    def __init__(self, *, vocab_size: int, hidden_size: int, tied: bool, dtype, device) -> None:
+    def __init__(self, *, vocab_size: int, hidden_size: int, tied: bool, dtype, device, name: str = "weight") -> None:
         super().__init__(dtype=dtype, device=device)
         self.vocab, self.hidden, self.tied = int(vocab_size), int(hidden_size), bool(tied)
+        self.name = name          # the tensor's name after the part's prefix (may be empty)
         self.weight: torch.Tensor | None = None
         self._embedding: TokenEmbedding | None = None
 
@@ -76,17 +90,17 @@ class LMHead(Part):
         self._embedding = embedding
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
-        return {"weight": TensorSpec((self.vocab, self.hidden), optional=self.tied)}
+        return {self.name: TensorSpec((self.vocab, self.hidden), optional=self.tied)}
 
     def load_tensor(self, name: str, tensor: torch.Tensor) -> None:
-        if name != "weight":
+        if name != self.name:
             raise KeyError(name)
         if self.weight is None:
             self.weight = self.new_storage((self.vocab, self.hidden), MATRIX)
         self.weight.copy_(tensor)
 
     def finalize(self, loaded: set[str]) -> None:
-        if "weight" not in loaded:
+        if self.name not in loaded:
             if not self.tied or self._embedding is None:
                 raise ValueError("the output head has no weight and is not tied to the embedding")
             self.weight = self._embedding.weight  # one tensor, not a copy

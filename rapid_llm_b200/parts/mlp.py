@@ -19,28 +19,29 @@ class SwiGLU(FeedForward):
     rides_norms = True
 
     def __init__(self, *, hidden_size: int, intermediate_size: int, dtype, device,
-                 gate_name: str = "gate_proj", up_name: str = "up_proj", down_name: str = "down_proj") -> None:
+                 gate_name: str = "gate_proj", up_name: str = "up_proj", down_name: str = "down_proj",
+                 suffix: str = ".weight") -> None:
         super().__init__(dtype=dtype, device=device)
         self.hidden, self.inter = int(hidden_size), int(intermediate_size)
-        self.names = (gate_name, up_name, down_name)
+        self.names = (gate_name + suffix, up_name + suffix, down_name + suffix)     # the tensors' names after the prefix
         self.gate_up = self.new_storage((2 * self.inter, self.hidden), MATRIX)
         self.down = self.new_storage((self.hidden, self.inter), MATRIX)
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
         gate, up, down = self.names
         return {
-            f"{gate}.weight": TensorSpec((self.inter, self.hidden)),
-            f"{up}.weight": TensorSpec((self.inter, self.hidden)),
-            f"{down}.weight": TensorSpec((self.hidden, self.inter)),
+            gate: TensorSpec((self.inter, self.hidden)),
+            up: TensorSpec((self.inter, self.hidden)),
+            down: TensorSpec((self.hidden, self.inter)),
         }
 
     def load_tensor(self, name: str, tensor: torch.Tensor) -> None:
         gate, up, down = self.names
-        if name == f"{gate}.weight":
+        if name == gate:
             self.gate_up[: self.inter].copy_(tensor)
-        elif name == f"{up}.weight":
+        elif name == up:
             self.gate_up[self.inter :].copy_(tensor)
-        elif name == f"{down}.weight":
+        elif name == down:
             self.down.copy_(tensor)
         else:
             raise KeyError(name)
@@ -61,6 +62,28 @@ class SwiGLU(FeedForward):
 
     def uses_libraries(self) -> set[str]:
         return {"gemm"} if self.dtype == torch.bfloat16 else set()
+
+
+@FEED_FORWARDS.register("clamped_glu")
+class ClampedGLU(SwiGLU):
+    """``down(g * sigmoid(alpha g) * (u + 1))`` with ``g = min(gate(x), limit)`` and ``u = clamp(up(x), -limit, limit)``:
+    a gated unit whose branches are bounded before they meet, the linear branch shifted by one.  Gate and up
+    share one product as in :class:`SwiGLU`; the activation is float32 arithmetic on the product's result."""
+
+    rides_norms = False
+
+    def __init__(self, *, hidden_size: int, intermediate_size: int, limit: float, alpha: float = 1.702, dtype, device,
+                 gate_name: str = "gate", up_name: str = "up", down_name: str = "down", suffix: str = "") -> None:
+        super().__init__(hidden_size=hidden_size, intermediate_size=intermediate_size, dtype=dtype, device=device,
+                         gate_name=gate_name, up_name=up_name, down_name=down_name, suffix=suffix)
+        self.limit, self.alpha = float(limit), float(alpha)
+
+    def forward(self, x, batch):
+        rows = x.shape[0]
+        wide = batch.workspace.get("ffn_gate_up", rows, 2 * self.inter, x.dtype)
+        gemm.linear(x, self.gate_up, wide, batch.fault)
+        act = kernels.clamped_glu(wide, batch.workspace.get("ffn_act", rows, self.inter, x.dtype), self.limit, self.alpha)
+        return gemm.linear(act, self.down, batch.workspace.get("ffn_out", rows, self.hidden, x.dtype), batch.fault)
 
 
 # activation name -> (number of learned scalars, kernel over [T, I] rows)

@@ -47,6 +47,18 @@ class RMSNorm(Norm):
             return None
         return gemm.FollowingNorm(residual, self.weight, self.eps, batch.workspace)
 
+    def join(self, y, residual, batch, name="stream_rows"):
+        """The norm on a sublayer's output: ``residual += norm(y)`` in float32; returns the new stream in the
+        engine's dtype (what the next sublayer reads)."""
+        out = batch.workspace.get(name, y.shape[0], self.size, y.dtype)
+        return kernels.join_rmsnorm(y, residual, self.weight, out, self.eps)
+
+    def of_stream(self, residual, batch, *, row_index=None, name="normed"):
+        """The norm of the float32 stream itself (rows picked by ``row_index``), in the engine's dtype."""
+        rows = residual.shape[0] if row_index is None else row_index.numel()
+        out = batch.workspace.get(name, rows, self.size, self.dtype, min_rows=None if row_index is None else 64)
+        return kernels.stream_rmsnorm(residual, self.weight, out, self.eps, row_index)
+
     def forward(self, x, residual, batch, *, mode, write_residual, row_index=None, name="normed", addend=None):
         """Norm of ``x`` (``FIRST``/``PLAIN``) or of ``x + residual`` (``ADD``).
 

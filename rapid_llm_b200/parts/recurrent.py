@@ -8,6 +8,8 @@ prompts and single decoded tokens alike:
   ``S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q``.
 * :class:`Retention` (``retention``) — a fixed decay per head, no correction:
   ``S <- gamma S + k v^T; o = S^T q``, queries and keys rotated by position.
+* :class:`Lightning` (``lightning``) — the same recurrence with SiLU on q, k and v, no rotation, and one norm
+  over the heads side by side: ``S <- gamma S + k v^T; o = S^T q``.
 * :class:`StateSpaceDual` (``state_space_dual``) — the selective state space in its recurrent form:
   ``S <- exp(-exp(A) dt) S + dt B x^T; y = S^T C + D x``.
 
@@ -247,6 +249,74 @@ class Retention(_Recurrent):
         normed = space.get("ret_normed", rows, cv, x.dtype)
         kernels.gated_norm(read, normed, group=self.vdim, gate=proj[:, 2 * cq + cv :], act=kernels.GATE_SILU, eps=self.eps)
         return gemm.linear(normed, self.o, space.get("ret_out", rows, self.hidden, x.dtype), batch.fault)
+
+
+@MIXERS.register("lightning")
+class Lightning(_Recurrent):
+    """Linear attention with a fixed decay per head: ``q = silu(W_q x)``, ``k = silu(W_k x)``, ``v = silu(W_v x)``,
+    per head ``S <- decay_h S + k v^T`` and ``o = S^T q`` with no other scale.  The heads side by side are divided by
+    the root mean square of the whole row and multiplied by ``norm`` (one weight per column), then by
+    ``sigmoid(W_g x)``, then projected.  The activations' results, the state and the read-out are float32."""
+
+    DEFAULT_NAMES = ("q", "k", "v", "g", "o", "norm")
+
+    def __init__(self, *, hidden_size: int, num_heads: int, key_dim: int, value_dim: int, decay, norm_eps: float,
+                 names: dict[str, str] | None = None, dtype, device) -> None:
+        super().__init__(dtype=dtype, device=device)
+        self._set_names(names)
+        self.hidden, self.h, self.dim, self.vdim = int(hidden_size), int(num_heads), int(key_dim), int(value_dim)
+        self.eps = float(norm_eps)
+        if len(decay) != self.h:
+            raise ValueError(f"lightning needs one decay per head, got {len(decay)} for {self.h} heads")
+        self.cq, self.cv = self.h * self.dim, self.h * self.vdim
+        self.state_size, self.tail_size = self.h * self.dim * self.vdim, 0
+        self.w_in = self.new_storage((2 * self.cq + 2 * self.cv, self.hidden), MATRIX)      # q | k | v | g
+        self.o = self.new_storage((self.hidden, self.cv), MATRIX)
+        self.norm = self.new_storage((self.cv,), VECTOR)
+        self.decay = torch.tensor([float(d) for d in decay], dtype=torch.float32).to(self.device)
+
+    def _tensors(self):
+        return (self.w_in, self.o, self.norm)
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        return self._named({
+            "q": TensorSpec((self.cq, self.hidden)),
+            "k": TensorSpec((self.cq, self.hidden)),
+            "v": TensorSpec((self.cv, self.hidden)),
+            "g": TensorSpec((self.cv, self.hidden)),
+            "o": TensorSpec((self.hidden, self.cv)),
+            "norm": TensorSpec((self.cv,), VECTOR, init="ones_normal"),
+        })
+
+    def load_tensor(self, name: str, tensor: torch.Tensor) -> None:
+        name = self._ours.get(name, "")
+        cq, cv = self.cq, self.cv
+        rows = {"q": (0, cq), "k": (cq, 2 * cq), "v": (2 * cq, 2 * cq + cv), "g": (2 * cq + cv, 2 * cq + 2 * cv)}
+        if name in rows:
+            self.w_in[rows[name][0] : rows[name][1]].copy_(tensor)
+        elif name == "o":
+            self.o.copy_(tensor)
+        elif name == "norm":
+            self.norm.copy_(tensor.to(torch.float32))
+        else:
+            raise KeyError(name)
+
+    def workspace_elements_per_token(self) -> int:
+        return 4 * self.w_in.shape[0] + self.hidden
+
+    def forward(self, x, batch, cache):
+        rows, space, f32 = x.shape[0], batch.workspace, torch.float32
+        S, _ = self._state_views(cache)
+        cq, cv = self.cq, self.cv
+        proj = gemm.linear(x, self.w_in, space.get("lightning_in", rows, self.w_in.shape[0], x.dtype), batch.fault)
+        qkv = kernels.activate_rows(proj[:, : 2 * cq + cv], space.get("lightning_qkv", rows, 2 * cq + cv, f32), act=True)
+        read = space.get("lightning_read", rows, cv, f32)
+        kernels.linear_scan(qkv[:, :cq], qkv[:, cq : 2 * cq], qkv[:, 2 * cq :], self.decay, read, S, batch,
+                            heads=self.h, kv_heads=self.h, dim=self.dim, vdim=self.vdim)
+        normed = space.get("lightning_normed", rows, cv, x.dtype)
+        kernels.gated_norm(read, normed, group=cv, gate=proj[:, 2 * cq + cv :], act=kernels.GATE_SIGMOID,
+                           weight=self.norm, eps=self.eps)
+        return gemm.linear(normed, self.o, space.get("lightning_out", rows, self.hidden, x.dtype), batch.fault)
 
 
 @MIXERS.register("state_space_dual")

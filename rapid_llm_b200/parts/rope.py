@@ -55,3 +55,20 @@ class NoPositions(PositionEncoding):
 
     def tables(self) -> tuple[torch.Tensor, torch.Tensor]:
         return self.cos, self.sin
+
+
+@POSITION_ENCODINGS.register("rotary_frequencies")
+class RotaryFrequencies(PositionEncoding):
+    """Rotation without tables: the float32 frequencies ``theta^(-2i / R)``, ``i < R / 2``; a kernel forms the angle
+    ``position * frequency`` and its sine and cosine itself, so no length bounds the positions."""
+
+    def __init__(self, *, rotary_dim: int, theta: float, max_positions: int, dtype, device) -> None:
+        super().__init__(dtype=dtype, device=device)
+        if rotary_dim % 2 or rotary_dim < 0:
+            raise ValueError(f"rotary_dim {rotary_dim} must be even and not negative")
+        self.rotary_dim, self.theta, self.max_positions = int(rotary_dim), float(theta), int(max_positions)
+        exponents = torch.arange(0, self.rotary_dim, 2, dtype=torch.float64) / max(self.rotary_dim, 1)
+        self.inv_freq = (float(theta) ** -exponents).to(torch.float32).to(self.device)
+
+    def tables(self) -> tuple[torch.Tensor, torch.Tensor]:
+        raise ValueError("this position encoding has no tables; its kernel computes the angles")

@@ -43,7 +43,7 @@ def build_parser() -> argparse.ArgumentParser:
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="most tokens live requests hold at any time (sizes the cache pool)")
     parser.add_argument("--page-size", type=int, default=16)
-    parser.add_argument("--max-live", type=int, default=8, help="requests live at a time")
+    parser.add_argument("--max-live", type=int, default=4, help="requests live at a time (state slots)")
     parser.add_argument("--device", default="cuda:0")
     return parser
 
@@ -93,7 +93,7 @@ class Replayer:
         return host
 
 
-def engine_config_for(model_config, dtype: str, max_tokens: int, page_size: int = 16, max_live: int = 8):
+def engine_config_for(model_config, dtype: str, max_tokens: int, page_size: int = 16, max_live: int = 4):
     """Engine sizes for a replay whose live requests hold at most ``max_tokens`` tokens."""
     from .config import EngineConfig, parse_dtype
 

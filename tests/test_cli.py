@@ -82,6 +82,6 @@ def test_replay_sizes_the_pool_from_max_tokens():
     tiny = engine_config_for(Qwen3Config.from_dict(TINY_A), "float32", 3)
     assert tiny.num_pages == 1 and tiny.max_seq_len == 16 and tiny.max_num_batched_tokens == 64
     args = build_parser().parse_args(["--model", "m", "--dtype", "float32", "--out", "o", "--max-tokens", "256"])
-    assert (args.page_size, args.max_live, args.device) == (16, 8, "cuda:0")
+    assert (args.page_size, args.max_live, args.device) == (16, 4, "cuda:0")
     with pytest.raises(SystemExit):
         build_parser().parse_args(["--model", "m", "--dtype", "float16", "--out", "o", "--max-tokens", "1"])
