@@ -48,14 +48,14 @@ __global__ void router_topk_kernel(const T* x, int x_stride, const float* __rest
     float acc = 0.0f;
     for (int k = lane; k < hidden; k += 32) acc = fmaf(wr[k], to_float(xr[k]), acc);
     acc = warp_sum(acc);
-    if (lane == 0) s[e] = moe_sigmoid(acc);
+    if (lane == 0) s[e] = acc;      // the logit: the choice is made on it (sigmoid keeps the order, and does not saturate into ties)
   }
   __syncwarp();
   if (scores_out)
-    for (int e = lane; e < experts; e += 32) scores_out[static_cast<size_t>(t) * experts + e] = s[e];
-  for (int g = lane; g < gates; g += 32) gate_out[static_cast<size_t>(t) * gates + g] = s[experts + g];
+    for (int e = lane; e < experts; e += 32) scores_out[static_cast<size_t>(t) * experts + e] = moe_sigmoid(s[e]);
+  for (int g = lane; g < gates; g += 32) gate_out[static_cast<size_t>(t) * gates + g] = moe_sigmoid(s[experts + g]);
   for (int j = 0; j < top; ++j) {
-    float best = -1.0f;
+    float best = -INFINITY;
     int best_e = 0x7fffffff;
     for (int e = lane; e < experts; e += 32) {
       const float v = s[e];
@@ -69,8 +69,8 @@ __global__ void router_topk_kernel(const T* x, int x_stride, const float* __rest
     }
     if (lane == 0) {
       ids[static_cast<size_t>(t) * top + j] = best_e;
-      weights[static_cast<size_t>(t) * top + j] = best;
-      s[best_e] = -2.0f;      // taken
+      weights[static_cast<size_t>(t) * top + j] = moe_sigmoid(best);
+      s[best_e] = -INFINITY;      // taken
     }
     __syncwarp();
   }

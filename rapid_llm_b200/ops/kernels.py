@@ -964,6 +964,8 @@ def causal_conv_silu(x: torch.Tensor, taps: torch.Tensor, bias: torch.Tensor | N
     slots, stride = _state_row(tail)
     if taps.shape[0] != channels or out.shape != (tokens, channels) or tail.shape[1] != (width - 1) * channels:
         raise KernelError("causal_conv_silu: shapes of x, taps, tail and out do not agree")
+    if width == 1:
+        slots = 1 << 30      # one tap reads no tail: any slot index is fine, whatever rows `tail` has
     _check(
         recurrent().rl_causal_conv_silu(
             dtype_tag(x.dtype), _ptr(x), _row_stride("x", x), 0, _ptr(taps), _ptr(bias), _ptr(tail), stride, 0,

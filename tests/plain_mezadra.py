@@ -131,11 +131,15 @@ def router_scores(h: torch.Tensor, w: dict, prefix: str) -> torch.Tensor:
     return torch.sigmoid(h @ w[prefix + "router"].T)
 
 
-def routed_experts(h: torch.Tensor, w: dict, prefix: str, mlp: dict) -> torch.Tensor:
+def routed_experts(h: torch.Tensor, w: dict, prefix: str, mlp: dict, margins: list | None = None) -> torch.Tensor:
     """Each token runs its ``top`` best experts on ``score * h`` (the score scales the input, scores are not
-    renormalised); a shared expert runs for every token, times ``sigmoid(sg h)``."""
+    renormalised); a shared expert runs for every token, times ``sigmoid(sg h)``.  ``margins`` receives, per
+    token, the gap between the last chosen and the first unchosen router logit over the logits' spread."""
     top = int(mlp["router"]["top"])
     scores = router_scores(h, w, prefix)
+    if margins is not None and top < scores.shape[1]:
+        logits = torch.sort(h @ w[prefix + "router"].T, dim=-1, descending=True).values
+        margins.extend(((logits[:, top - 1] - logits[:, top]) / (logits.std(-1) + 1e-9)).tolist())
     chosen = torch.topk(scores, top, dim=-1).indices
     out = torch.zeros(h.shape[0], w[prefix + "e0.down"].shape[0], dtype=F)
     for t in range(h.shape[0]):
@@ -146,15 +150,16 @@ def routed_experts(h: torch.Tensor, w: dict, prefix: str, mlp: dict) -> torch.Te
     return out
 
 
-def feed_forward(h: torch.Tensor, w: dict, prefix: str, mlp: dict) -> torch.Tensor:
+def feed_forward(h: torch.Tensor, w: dict, prefix: str, mlp: dict, margins: list | None = None) -> torch.Tensor:
     if mlp["kind"] == "dense":
         return clamped_glu(h, w, prefix, float(mlp["limit"]))
-    return routed_experts(h, w, prefix, mlp)
+    return routed_experts(h, w, prefix, mlp, margins)
 
 
 # ------------------------------------------------------------------ the model
-def forward(config: dict, w: dict, tokens, collect: list | None = None) -> torch.Tensor:
-    """Logits ``[T, vocab]`` of one sequence; ``collect`` receives the stream after every layer."""
+def forward(config: dict, w: dict, tokens, collect: list | None = None, margins: list | None = None) -> torch.Tensor:
+    """Logits ``[T, vocab]`` of one sequence; ``collect`` receives the stream after every layer, ``margins`` how
+    clearly every router decision fell (see :func:`routed_experts`)."""
     eps = float(config["norm"]["eps"])
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)] * float(config["embedding"]["scale"])
     first_values = None
@@ -171,7 +176,22 @@ def forward(config: dict, w: dict, tokens, collect: list | None = None) -> torch
             raise ValueError(layer["type"])
         x = x + rms_norm(mixed, eps, w[prefix + "norm1"])
         if layer.get("mlp") is not None:
-            x = x + rms_norm(feed_forward(x, w, prefix + "mlp.", layer["mlp"]), eps, w[prefix + "norm2"])
+            x = x + rms_norm(feed_forward(x, w, prefix + "mlp.", layer["mlp"], margins), eps, w[prefix + "norm2"])
         if collect is not None:
             collect.append(x.clone())
     return rms_norm(x, eps, w["final.norm"]) @ w["head"].T
+
+
+def greedy(config: dict, w: dict, prompt, steps: int) -> list[int]:
+    """The ``steps`` tokens that always taking the largest logit produces after ``prompt``."""
+    tokens = list(prompt)
+    for _ in range(steps):
+        tokens.append(int(forward(config, w, tokens)[-1].argmax()))
+    return tokens[len(prompt):]
+
+
+def clear_margin(config: dict, w: dict, tokens) -> float:
+    """The narrowest router decision of the sequence (infinite for a model without routers)."""
+    margins: list = []
+    forward(config, w, tokens, margins=margins)
+    return min(margins) if margins else math.inf
