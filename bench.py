@@ -590,7 +590,7 @@ def main() -> int:
     parser.add_argument("--context", type=int, default=CONTEXT, help="longest sequence the engine is set up for")
     parser.add_argument("--points", default="1,64", help="other batch sizes decoded beside --batch")
     parser.add_argument("--sizes", default="2048,4096", help="widths of the models of --workload kopatar")
-    parser.add_argument("--workload", choices=["decode", "serve", "kopatar"], default="decode", help="decode: the benchmark "
+    parser.add_argument("--workload", choices=["decode", "serve", "kopatar", "mezadra"], default="decode", help="decode: the benchmark "
                         "(timed decode steps, a prefill, the points); serve: continuous batching of --requests "
                         "prompts of mixed lengths through generate()")
     parser.add_argument("--requests", type=int, default=64, help="requests of the serve workload")
@@ -624,6 +624,15 @@ def main() -> int:
 
         with ClockSampler() as clocks:
             result = kopatar_run([int(size) for size in args.sizes.split(",") if size], measured_peaks()["hbm_gbs"])
+        result["clocks"] = clocks.summary()
+        print(json.dumps(result))
+        return 0
+    if args.workload == "mezadra":
+        # the design with softmax and linear attention and routed experts beside Qwen3 at equal sizes, and its kernels alone
+        from rapid_llm_b200.ops.mezadra_compare import run as mezadra_run
+
+        with ClockSampler() as clocks:
+            result = mezadra_run([int(size) for size in args.sizes.split(",") if size], measured_peaks()["hbm_gbs"])
         result["clocks"] = clocks.summary()
         print(json.dumps(result))
         return 0

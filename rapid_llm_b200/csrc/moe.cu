@@ -25,35 +25,90 @@ constexpr int kMoeTileM = 32;     // pairs per tile
 constexpr int kMoeTileN = 64;     // output columns per block
 constexpr int kMoeTileK = 32;
 constexpr int kMoeThreads = 256;
+constexpr int kMoeWideM = 64;     // pairs per tile of the pipelined bfloat16 kernel
+constexpr int kMoeWideK = 64;
+constexpr int kMoeStages = 3;
 
 __device__ __forceinline__ float moe_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
 
 // ------------------------------------------------------------------ router
-// One warp per token.  scores live in shared memory ([warps][E + G]).
+// One block per kRouterTokens tokens; a warp takes rows e = warp, warp + warps, ... of W_r and forms the row's
+// product with each of the block's tokens at once (the row is read once for all of them).  A product's sum
+// runs over k = lane, lane + 32, ... and then down the warp's tree, whatever else is in the block, so a token's
+// logits do not depend on the batch.  The logits meet in shared memory ([tokens][E + G]); warp t then picks
+// token t's experts.
+constexpr int kRouterTokens = 4;
+constexpr int kRouterWarps = 8;
+
+__device__ __forceinline__ void router_load4(const float* p, float (&v)[4]) {
+  const float4 f = *reinterpret_cast<const float4*>(p);
+  v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+}
+__device__ __forceinline__ void router_load4(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 packed = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&packed);
+  const float2 lo = __bfloat1622float2(h[0]), hi = __bfloat1622float2(h[1]);
+  v[0] = lo.x; v[1] = lo.y; v[2] = hi.x; v[3] = hi.y;
+}
+
 template <typename T>
-__global__ void router_topk_kernel(const T* x, int x_stride, const float* __restrict__ w, int hidden, int experts,
-                                   int gates, int top, int* __restrict__ ids, float* __restrict__ weights,
-                                   float* __restrict__ gate_out, float* __restrict__ scores_out, int tokens) {
-  extern __shared__ float moe_scores[];
+__global__ void __launch_bounds__(kRouterWarps * 32)
+router_topk_kernel(const T* x, int x_stride, const float* __restrict__ w, int hidden, int experts,
+                   int gates, int top, int* __restrict__ ids, float* __restrict__ weights,
+                   float* __restrict__ gate_out, float* __restrict__ scores_out, int tokens, int wide) {
+  extern __shared__ float moe_scores[];      // [kRouterTokens][experts + gates]
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-  pdl_wait();
-  if (t >= tokens) return;
+  const int t0 = blockIdx.x * kRouterTokens;
   const int rows = experts + gates;
-  float* s = moe_scores + static_cast<size_t>(warp) * rows;
-  const T* xr = x + static_cast<size_t>(t) * x_stride;
-  for (int e = 0; e < rows; ++e) {
+  pdl_wait();
+  const T* xr[kRouterTokens];
+#pragma unroll
+  for (int i = 0; i < kRouterTokens; ++i)
+    xr[i] = x + static_cast<size_t>(min(t0 + i, tokens - 1)) * x_stride;      // rows past the end repeat the last one
+  for (int e = warp; e < rows; e += kRouterWarps) {
     const float* wr = w + static_cast<size_t>(e) * hidden;
-    float acc = 0.0f;
-    for (int k = lane; k < hidden; k += 32) acc = fmaf(wr[k], to_float(xr[k]), acc);
-    acc = warp_sum(acc);
-    if (lane == 0) s[e] = acc;      // the logit: the choice is made on it (sigmoid keeps the order, and does not saturate into ties)
+    float acc[kRouterTokens];
+#pragma unroll
+    for (int i = 0; i < kRouterTokens; ++i) acc[i] = 0.0f;
+    if (wide) {
+      // four neighbouring k a lane and step (16- and 8-byte loads), eight steps in flight
+#pragma unroll 8
+      for (int k = lane * 4; k < hidden; k += 128) {
+        const float4 wv = *reinterpret_cast<const float4*>(wr + k);
+#pragma unroll
+        for (int i = 0; i < kRouterTokens; ++i) {
+          float xv[4];
+          router_load4(xr[i] + k, xv);
+          acc[i] = fmaf(wv.x, xv[0], acc[i]);
+          acc[i] = fmaf(wv.y, xv[1], acc[i]);
+          acc[i] = fmaf(wv.z, xv[2], acc[i]);
+          acc[i] = fmaf(wv.w, xv[3], acc[i]);
+        }
+      }
+    } else {
+#pragma unroll 4
+      for (int k = lane; k < hidden; k += 32) {
+        const float wv = wr[k];
+#pragma unroll
+        for (int i = 0; i < kRouterTokens; ++i) acc[i] = fmaf(wv, to_float(xr[i][k]), acc[i]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kRouterTokens; ++i) {
+      const float total = warp_sum(acc[i]);
+      // the logit: the choice is made on it (sigmoid keeps the order, and does not saturate into ties)
+      if (lane == 0) moe_scores[i * rows + e] = total;
+    }
   }
-  __syncwarp();
+  __syncthreads();
+  if (warp >= kRouterTokens || t0 + warp >= tokens) return;
+  const int t = t0 + warp;
+  float* s = moe_scores + warp * rows;
   if (scores_out)
     for (int e = lane; e < experts; e += 32) scores_out[static_cast<size_t>(t) * experts + e] = moe_sigmoid(s[e]);
   for (int g = lane; g < gates; g += 32) gate_out[static_cast<size_t>(t) * gates + g] = moe_sigmoid(s[experts + g]);
+  __syncwarp();
   for (int j = 0; j < top; ++j) {
     float best = -INFINITY;
     int best_e = 0x7fffffff;
@@ -67,6 +122,7 @@ __global__ void router_topk_kernel(const T* x, int x_stride, const float* __rest
       const int other_e = __shfl_xor_sync(0xffffffffu, best_e, offset);
       if (other > best || (other == best && other_e < best_e)) { best = other; best_e = other_e; }
     }
+    if (best_e == 0x7fffffff) best_e = 0;      // every logit left is not a number: keep the index inside the table
     if (lane == 0) {
       ids[static_cast<size_t>(t) * top + j] = best_e;
       weights[static_cast<size_t>(t) * top + j] = moe_sigmoid(best);
@@ -80,7 +136,7 @@ __global__ void router_topk_kernel(const T* x, int x_stride, const float* __rest
 // One block.  meta: [0] tiles, then per tile (expert, first place, rows).  `sorted` [pairs] receives pair
 // indices expert by expert.  `place_of` [pairs]: where pair i went (the inverse of sorted).
 __global__ void moe_plan_kernel(const int* __restrict__ ids, int pairs, int experts, int* __restrict__ sorted,
-                                int* __restrict__ place_of, int* __restrict__ meta, int max_tiles,
+                                int* __restrict__ place_of, int* __restrict__ meta, int max_tiles, int tile_m,
                                 int* __restrict__ fault) {
   extern __shared__ int moe_counts[];      // [experts] counts, [experts] cursors
   pdl_trigger();
@@ -98,11 +154,11 @@ __global__ void moe_plan_kernel(const int* __restrict__ ids, int pairs, int expe
     int at = 0, tiles = 0;
     for (int e = 0; e < experts; ++e) {
       cursor[e] = at;
-      for (int row = 0; row < counts[e]; row += kMoeTileM) {
+      for (int row = 0; row < counts[e]; row += tile_m) {
         if (tiles < max_tiles) {
           meta[1 + 3 * tiles] = e;
           meta[2 + 3 * tiles] = at + row;
-          meta[3 + 3 * tiles] = min(kMoeTileM, counts[e] - row);
+          meta[3 + 3 * tiles] = min(tile_m, counts[e] - row);
         }
         ++tiles;
       }
@@ -342,6 +398,161 @@ grouped_linear_mma_kernel(const __nv_bfloat16* a, int a_stride, const __nv_bfloa
   }
 }
 
+// ------------------------------------------------------------------ the same, pipelined (bfloat16, aligned operands)
+// Tiles of 64 pairs x 64 columns (twice 64 weight rows when gated), k in chunks of 64 through a ring of three
+// stages filled by cp.async (16 bytes a copy; rows of pairs beyond the tile and columns beyond k arrive as zeros),
+// fragments by ldmatrix.  8 warps as 2 x 4: a warp owns 32 rows x 16 columns.  Wants k a multiple of 8 and
+// 16-byte aligned operands; the host falls back to the plain tiles otherwise.
+__device__ __forceinline__ void moe_cp_async16(void* dst, const void* src, bool valid) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void moe_ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+
+template <bool kGated>
+constexpr int moe_wide_smem_bytes() {
+  return kMoeStages * (kMoeWideM + (kGated ? 2 : 1) * kMoeTileN) * (kMoeWideK + 8) * 2;
+}
+
+template <bool kGated>
+__global__ void __launch_bounds__(kMoeThreads)
+grouped_linear_wide_kernel(const __nv_bfloat16* a, int a_stride, const __nv_bfloat16* __restrict__ w,
+                           const int* __restrict__ sorted, const int* __restrict__ meta,
+                           const float* __restrict__ pair_weight, int top, int by_token, int n, int k,
+                           __nv_bfloat16* out_act, float* out_y) {
+  constexpr int kStride = kMoeWideK + 8;
+  constexpr int kWRows = (kGated ? 2 : 1) * kMoeTileN;
+  constexpr int kStageElems = (kMoeWideM + kWRows) * kStride;
+  extern __shared__ __align__(16) unsigned char moe_wide_smem[];
+  __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(moe_wide_smem);
+  __shared__ int s_pair[kMoeWideM];
+  pdl_trigger();
+  pdl_wait();
+  const int tile = blockIdx.y;
+  if (tile >= meta[0]) return;
+  const int expert = meta[1 + 3 * tile], place0 = meta[2 + 3 * tile], rows = meta[3 + 3 * tile];
+  const int n0 = blockIdx.x * kMoeTileN;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid < kMoeWideM) s_pair[tid] = tid < rows ? sorted[place0 + tid] : -1;
+  __syncthreads();
+  const size_t w_rows = kGated ? 2 * static_cast<size_t>(n) : static_cast<size_t>(n);
+  const __nv_bfloat16* we = w + static_cast<size_t>(expert) * w_rows * k;
+
+  // what this thread copies per stage: 2 pieces of the pairs' rows, 2 (4) pieces of the weight rows
+  const __nv_bfloat16* a_src[2];
+  bool a_ok[2];
+  int a_dst[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int idx = tid + i * kMoeThreads, r = idx >> 3, c = (idx & 7) * 8;
+    const int pair = s_pair[r];
+    a_ok[i] = pair >= 0;
+    const size_t row = a_ok[i] ? (by_token ? static_cast<size_t>(pair / top) : static_cast<size_t>(place0 + r)) : 0;
+    a_src[i] = a + row * a_stride + c;
+    a_dst[i] = r * kStride + c;
+  }
+  constexpr int kWPieces = kWRows * 8 / kMoeThreads;
+  const __nv_bfloat16* w_src[kWPieces];
+  bool w_ok[kWPieces];
+  int w_dst[kWPieces];
+#pragma unroll
+  for (int i = 0; i < kWPieces; ++i) {
+    const int idx = tid + i * kMoeThreads, r = idx >> 3, c = (idx & 7) * 8;
+    const int col = n0 + (r & (kMoeTileN - 1));
+    w_ok[i] = col < n;
+    const size_t row = w_ok[i] ? static_cast<size_t>(col) + (r >= kMoeTileN ? static_cast<size_t>(n) : 0) : 0;
+    w_src[i] = we + row * k + c;
+    w_dst[i] = (kMoeWideM + r) * kStride + c;
+  }
+  const int chunks = (k + kMoeWideK - 1) / kMoeWideK;
+  auto fill = [&](int chunk) {
+    __nv_bfloat16* stage = ring + (chunk % kMoeStages) * kStageElems;
+    const int k0 = chunk * kMoeWideK;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const bool ok = a_ok[i] && k0 + ((tid + i * kMoeThreads) & 7) * 8 < k;
+      moe_cp_async16(stage + a_dst[i], ok ? a_src[i] + k0 : a, ok);
+    }
+#pragma unroll
+    for (int i = 0; i < kWPieces; ++i) {
+      const bool ok = w_ok[i] && k0 + ((tid + i * kMoeThreads) & 7) * 8 < k;
+      moe_cp_async16(stage + w_dst[i], ok ? w_src[i] + k0 : w, ok);
+    }
+  };
+#pragma unroll
+  for (int s = 0; s < kMoeStages - 1; ++s) {
+    if (s < chunks) fill(s);
+    asm volatile("cp.async.commit_group;\n" ::);
+  }
+  const int wm = warp & 1, wn = warp >> 1;      // 2 x 4 warps: 32 rows x 16 columns each
+  float acc[kGated ? 2 : 1][2][2][4];
+#pragma unroll
+  for (int g = 0; g < (kGated ? 2 : 1); ++g)
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[g][mt][nt][c] = 0.0f;
+  for (int chunk = 0; chunk < chunks; ++chunk) {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(kMoeStages - 2));
+    __syncthreads();      // the chunk has landed for every thread, and the stage about to be refilled has been read
+    if (chunk + kMoeStages - 1 < chunks) fill(chunk + kMoeStages - 1);
+    asm volatile("cp.async.commit_group;\n" ::);
+    const __nv_bfloat16* sa = ring + (chunk % kMoeStages) * kStageElems;
+    const __nv_bfloat16* sw = sa + kMoeWideM * kStride;
+#pragma unroll
+    for (int ks = 0; ks < kMoeWideK; ks += 16) {
+      uint32_t af[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+        moe_ldmatrix_x4(af[mt], sa + (wm * 32 + mt * 16 + (lane & 15)) * kStride + ks + (lane >> 4) * 8);
+#pragma unroll
+      for (int g = 0; g < (kGated ? 2 : 1); ++g) {
+        uint32_t bf[4];      // (n 0-7, k 0-7), (n 0-7, k 8-15), (n 8-15, k 0-7), (n 8-15, k 8-15)
+        moe_ldmatrix_x4(bf, sw + (g * kMoeTileN + wn * 16 + (lane & 7) + ((lane >> 4) << 3)) * kStride + ks +
+                                ((lane >> 3) & 1) * 8);
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          moe_mma_bf16(acc[g][mt][0], af[mt], bf[0], bf[1]);
+          moe_mma_bf16(acc[g][mt][1], af[mt], bf[2], bf[3]);
+        }
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::);
+  const int gr = lane >> 2, q = (lane & 3) * 2;
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int row = wm * 32 + mt * 16 + gr + 8 * half;
+      const int pair = s_pair[row];
+      if (pair < 0) continue;
+      const float scale = (kGated && pair_weight) ? pair_weight[pair] : 1.0f;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int col = n0 + wn * 16 + nt * 8 + q + c;
+          if (col >= n) continue;
+          if constexpr (kGated) {
+            const float g = acc[0][mt][nt][2 * half + c] * scale, u = acc[1][mt][nt][2 * half + c] * scale;
+            out_act[static_cast<size_t>(place0 + row) * n + col] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+          } else {
+            out_y[static_cast<size_t>(pair) * n + col] = acc[0][mt][nt][2 * half + c];
+          }
+        }
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------ combine
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ y, int top, const T* shared, const float* __restrict__ gate,
@@ -364,7 +575,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, int top, const T
 
 extern "C" {
 
-int rl_moe_tile_rows() { return rl::kMoeTileM; }
+int rl_moe_tile_rows(int wide) { return wide ? rl::kMoeWideM : rl::kMoeTileM; }
 
 int rl_router_topk(int dtype, const void* x, int x_stride, const float* w, int hidden, int experts, int gates, int top,
                    int* ids, float* weights, float* gate_out, float* scores_out, int tokens, int pdl,
@@ -372,32 +583,72 @@ int rl_router_topk(int dtype, const void* x, int x_stride, const float* w, int h
   if (tokens == 0) return 0;
   if (experts < 1 || top < 1 || top > experts || gates < 0 || (gates > 0 && gate_out == nullptr) || hidden < 1)
     return static_cast<int>(cudaErrorInvalidValue);
-  const int warps = 4;
-  const size_t smem = static_cast<size_t>(warps) * (experts + gates) * sizeof(float);
+  const size_t smem = static_cast<size_t>(rl::kRouterTokens) * (experts + gates) * sizeof(float);
   if (smem > 48 * 1024) return static_cast<int>(cudaErrorInvalidValue);
+  // whole rows in 16-byte pieces: which order a row's sum runs in depends on the sizes and addresses alone
+  const int wide = hidden % 4 == 0 && x_stride % 4 == 0 &&
+                   ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
   RL_DISPATCH_DTYPE(dtype, {
-    return rl::launch_kernel(rl::router_topk_kernel<scalar_t>, dim3((tokens + warps - 1) / warps), dim3(warps * 32),
+    return rl::launch_kernel(rl::router_topk_kernel<scalar_t>,
+                             dim3((tokens + rl::kRouterTokens - 1) / rl::kRouterTokens), dim3(rl::kRouterWarps * 32),
                              smem, stream, pdl != 0, static_cast<const scalar_t*>(x), x_stride, w, hidden, experts,
-                             gates, top, ids, weights, gate_out, scores_out, tokens);
+                             gates, top, ids, weights, gate_out, scores_out, tokens, wide);
   });
   return 0;
 }
 
 int rl_moe_plan(const int* ids, int pairs, int experts, int* sorted, int* place_of, int* meta, int max_tiles,
-                int* fault, int pdl, cudaStream_t stream) {
+                int tile_m, int* fault, int pdl, cudaStream_t stream) {
   if (pairs == 0) return 0;
   const size_t smem = 2 * static_cast<size_t>(experts) * sizeof(int);
-  if (experts < 1 || smem > 48 * 1024 || max_tiles < 1) return static_cast<int>(cudaErrorInvalidValue);
+  if (experts < 1 || smem > 48 * 1024 || max_tiles < 1 || (tile_m != rl::kMoeTileM && tile_m != rl::kMoeWideM))
+    return static_cast<int>(cudaErrorInvalidValue);
   return rl::launch_kernel(rl::moe_plan_kernel, dim3(1), dim3(1024), smem, stream, pdl != 0, ids, pairs, experts,
-                           sorted, place_of, meta, max_tiles, fault);
+                           sorted, place_of, meta, max_tiles, tile_m, fault);
 }
 
 // a: engine dtype rows; w: [experts, (gated ? 2 n : n), k] engine dtype; gated: out_act [pairs, n] engine dtype by
 // place; else out_y [pairs, n] float32 by pair.
+}  // extern "C"
+
+template <bool kGated>
+static int launch_grouped_wide(dim3 grid, cudaStream_t stream, bool pdl, const __nv_bfloat16* a, int a_stride,
+                               const __nv_bfloat16* w, const int* sorted, const int* meta, const float* pair_weight,
+                               int top, int by_token, int n, int k, __nv_bfloat16* out_act, float* out_y) {
+  static bool configured = false;
+  auto kernel = rl::grouped_linear_wide_kernel<kGated>;
+  constexpr int smem = rl::moe_wide_smem_bytes<kGated>();
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  return rl::launch_kernel(kernel, grid, dim3(rl::kMoeThreads), smem, stream, pdl, a, a_stride, w, sorted, meta,
+                           pair_weight, top, by_token, n, k, out_act, out_y);
+}
+
+extern "C" {
+
+// tile_m: the rows of a tile the plan was made with; kMoeWideM selects the pipelined bfloat16 kernel.
 int rl_grouped_linear(int dtype, const void* a, int a_stride, const void* w, const int* sorted, const int* meta,
                       const float* pair_weight, int top, int by_token, int n, int k, int gated, void* out_act,
-                      float* out_y, int max_tiles, int pdl, cudaStream_t stream) {
+                      float* out_y, int max_tiles, int tile_m, int pdl, cudaStream_t stream) {
   if (max_tiles == 0) return 0;
+  if (tile_m == rl::kMoeWideM) {
+    using bf = __nv_bfloat16;
+    if (dtype != rl::kBF16 || k % 8 != 0 || a_stride % 8 != 0 || n < 1 || max_tiles > 65535 ||
+        ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) & 15) != 0)
+      return static_cast<int>(cudaErrorInvalidValue);
+    const dim3 wide_grid((n + rl::kMoeTileN - 1) / rl::kMoeTileN, max_tiles);
+    if (gated)
+      return launch_grouped_wide<true>(wide_grid, stream, pdl != 0, static_cast<const bf*>(a), a_stride,
+                                       static_cast<const bf*>(w), sorted, meta, pair_weight, top, by_token, n, k,
+                                       static_cast<bf*>(out_act), out_y);
+    return launch_grouped_wide<false>(wide_grid, stream, pdl != 0, static_cast<const bf*>(a), a_stride,
+                                      static_cast<const bf*>(w), sorted, meta, pair_weight, top, by_token, n, k,
+                                      static_cast<bf*>(out_act), out_y);
+  }
+  if (tile_m != rl::kMoeTileM) return static_cast<int>(cudaErrorInvalidValue);
   if (n < 1 || k < 1 || top < 1 || (gated && out_act == nullptr) || (!gated && out_y == nullptr) || max_tiles > 65535)
     return static_cast<int>(cudaErrorInvalidValue);
   const dim3 grid((n + rl::kMoeTileN - 1) / rl::kMoeTileN, max_tiles), block(rl::kMoeThreads);

@@ -1148,9 +1148,10 @@ def moe_lib() -> ctypes.CDLL:
         lib = load_library("moe")
         lib.rl_router_topk.argtypes = [c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                        c_void_p, c_void_p, c_int, c_int, c_void_p]
-        lib.rl_moe_plan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p]
+        lib.rl_moe_plan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]
+        lib.rl_moe_tile_rows.argtypes = [c_int]
         lib.rl_grouped_linear.argtypes = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                          c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]
+                                          c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         lib.rl_moe_combine.argtypes = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                                        c_void_p]
         for name in ("rl_router_topk", "rl_moe_plan", "rl_grouped_linear", "rl_moe_combine", "rl_moe_tile_rows"):
@@ -1159,9 +1160,19 @@ def moe_lib() -> ctypes.CDLL:
     return _MOE_LIB
 
 
-def moe_max_tiles(pairs: int, experts: int) -> int:
+def moe_tile_rows(wide: bool) -> int:
+    """Pairs per tile: of the plain tiles, or of the pipelined bfloat16 kernel's (``wide``)."""
+    return int(moe_lib().rl_moe_tile_rows(int(bool(wide))))
+
+
+def moe_wide_takes(dtype: torch.dtype, *inner_sizes: int) -> bool:
+    """Whether the pipelined bfloat16 kernel takes products with these inner sizes (16-byte rows)."""
+    return dtype == torch.bfloat16 and all(size % 8 == 0 for size in inner_sizes)
+
+
+def moe_max_tiles(pairs: int, experts: int, wide: bool = False) -> int:
     """Most tiles the (token, expert) pairs of a step can fall into."""
-    return -(-int(pairs) // int(moe_lib().rl_moe_tile_rows())) + int(experts)
+    return -(-int(pairs) // moe_tile_rows(wide)) + int(experts)
 
 
 def router_topk(x: torch.Tensor, weight: torch.Tensor, *, experts: int, top: int, ids: torch.Tensor,
@@ -1183,23 +1194,24 @@ def router_topk(x: torch.Tensor, weight: torch.Tensor, *, experts: int, top: int
 
 
 def moe_plan(ids: torch.Tensor, experts: int, sorted_pairs: torch.Tensor, place_of: torch.Tensor, meta: torch.Tensor,
-             fault: torch.Tensor) -> int:
-    """Groups the pairs ``ids [T, top]`` by expert on the device; returns the most tiles there can be."""
+             fault: torch.Tensor, wide: bool = False) -> int:
+    """Groups the pairs ``ids [T, top]`` by expert on the device, in tiles of :func:`moe_tile_rows` pairs; returns the
+    most tiles there can be.  The products over the plan must be asked for with the same ``wide``."""
     _need_cuda(ids, sorted_pairs, place_of, meta, fault)
     for name, tensor in (("ids", ids), ("sorted_pairs", sorted_pairs), ("place_of", place_of), ("meta", meta)):
         _expect(name, tensor, torch.int32), _contig(name, tensor)
     pairs = ids.numel()
-    max_tiles = moe_max_tiles(pairs, experts)
+    max_tiles = moe_max_tiles(pairs, experts, wide)
     if sorted_pairs.numel() < pairs or place_of.numel() < pairs or meta.numel() < 1 + 3 * max_tiles:
         raise KernelError("moe_plan: the tables are too small")
     _check(moe_lib().rl_moe_plan(_ptr(ids), pairs, experts, _ptr(sorted_pairs), _ptr(place_of), _ptr(meta), max_tiles,
-                                 _ptr(fault), int(PDL), _stream()), "moe_plan")
+                                 moe_tile_rows(wide), _ptr(fault), int(PDL), _stream()), "moe_plan")
     return max_tiles
 
 
 def grouped_linear(a: torch.Tensor, weight: torch.Tensor, sorted_pairs: torch.Tensor, meta: torch.Tensor, *, top: int,
                    by_token: bool, max_tiles: int, pair_weight: torch.Tensor | None = None,
-                   out_act: torch.Tensor | None = None, out_y: torch.Tensor | None = None) -> None:
+                   out_act: torch.Tensor | None = None, out_y: torch.Tensor | None = None, wide: bool = False) -> None:
     """Products over the pairs grouped by expert: ``weight [E, N or 2 N, K]``.  With ``out_act`` (engine dtype,
     by place) the weight is gate rows then up rows and ``out_act = silu(w g) * (w u)`` with the pair's weight ``w``;
     with ``out_y`` (float32, by pair) the plain product.  ``a`` rows are found by token (pair // top) or by place."""
@@ -1214,7 +1226,8 @@ def grouped_linear(a: torch.Tensor, weight: torch.Tensor, sorted_pairs: torch.Te
         raise KernelError("grouped_linear: the result's width does not fit the weight")
     _check(moe_lib().rl_grouped_linear(dtype_tag(a.dtype), _ptr(a), _row_stride("a", a), _ptr(weight), _ptr(sorted_pairs),
                                        _ptr(meta), _ptr(pair_weight), int(top), int(by_token), n, a.shape[1], int(gated),
-                                       _ptr(out_act), _ptr(out_y), int(max_tiles), int(PDL), _stream()), "grouped_linear")
+                                       _ptr(out_act), _ptr(out_y), int(max_tiles), moe_tile_rows(wide), int(PDL), _stream()),
+           "grouped_linear")
 
 
 def moe_combine(y: torch.Tensor, top: int, out: torch.Tensor, shared: torch.Tensor | None = None,

@@ -117,14 +117,15 @@ class RoutedExperts(FeedForward):
         kernels.router_topk(x, self.router, experts=experts, top=top, ids=ids, weights=weights, gates=gates)
         order = space.get("moe_sorted", tokens, top, i32).view(-1)
         place = space.get("moe_place", tokens, top, i32).view(-1)
+        wide = kernels.moe_wide_takes(x.dtype, self.hidden, self.inter)      # the pipelined bfloat16 tiles
         most = kernels.moe_max_tiles(max(space.max_tokens, tokens) * top, experts)
         meta = space.get("moe_meta", 1, 1 + 3 * most, i32, min_rows=1).view(-1)
-        max_tiles = kernels.moe_plan(ids, experts, order, place, meta, batch.fault)
+        max_tiles = kernels.moe_plan(ids, experts, order, place, meta, batch.fault, wide=wide)
         act = space.get("moe_act", tokens, top * self.inter, x.dtype).view(pairs, self.inter)
         kernels.grouped_linear(x, self.gate_up, order, meta, top=top, by_token=True, max_tiles=max_tiles,
-                               pair_weight=weights.view(-1), out_act=act)
+                               pair_weight=weights.view(-1), out_act=act, wide=wide)
         each = space.get("moe_each", tokens, top * self.hidden, f32).view(pairs, self.hidden)
-        kernels.grouped_linear(act, self.down, order, meta, top=top, by_token=False, max_tiles=max_tiles, out_y=each)
+        kernels.grouped_linear(act, self.down, order, meta, top=top, by_token=False, max_tiles=max_tiles, out_y=each, wide=wide)
         shared = None if self.shared is None else self.shared.forward(x, batch)
         out = space.get("moe_out", tokens, self.hidden, x.dtype)
         return kernels.moe_combine(each, top, out, shared=shared, gate=gates)

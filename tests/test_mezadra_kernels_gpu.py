@@ -14,11 +14,17 @@ def _silu(x):
     return x * torch.sigmoid(x)
 
 
+@pytest.mark.parametrize("wide", [False, True])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("tokens,experts,top,hidden,inter", [(300, 40, 3, 64, 24), (37, 5, 2, 50, 22), (1, 3, 3, 32, 8), (200, 1, 1, 40, 16)])
-def test_products_over_pairs_grouped_by_expert(tokens, experts, top, hidden, inter, dtype):
-    """Given choices and weights, plan + gated product + down product + sum equal the experts run pair by pair."""
+@pytest.mark.parametrize("tokens,experts,top,hidden,inter", [(300, 40, 3, 64, 24), (37, 5, 2, 50, 22), (1, 3, 3, 32, 8), (200, 1, 1, 40, 16),
+                                                             (150, 2, 2, 200, 72)])
+def test_products_over_pairs_grouped_by_expert(tokens, experts, top, hidden, inter, dtype, wide):
+    """Given choices and weights, plan + gated product + down product + sum equal the experts run pair by pair; on the
+    plain tiles and on the pipelined bfloat16 ones (``wide``; inner sizes that are no multiples of their chunk too)."""
     from rapid_llm_b200.ops import kernels
+
+    if wide and not kernels.moe_wide_takes(dtype, hidden, inter):
+        pytest.skip("the pipelined tiles take bfloat16 with 16-byte rows")
 
     g = torch.Generator().manual_seed(tokens + experts)
     x = torch.randn(tokens, hidden, generator=g).to(dtype).to(DEVICE)
@@ -32,12 +38,12 @@ def test_products_over_pairs_grouped_by_expert(tokens, experts, top, hidden, int
     pairs = tokens * top
     order = torch.empty(pairs, dtype=torch.int32, device=DEVICE)
     place = torch.empty(pairs, dtype=torch.int32, device=DEVICE)
-    meta = torch.zeros(1 + 3 * kernels.moe_max_tiles(pairs, experts), dtype=torch.int32, device=DEVICE)
-    max_tiles = kernels.moe_plan(ids, experts, order, place, meta, fault)
+    meta = torch.zeros(1 + 3 * kernels.moe_max_tiles(pairs, experts, wide), dtype=torch.int32, device=DEVICE)
+    max_tiles = kernels.moe_plan(ids, experts, order, place, meta, fault, wide=wide)
     act = torch.empty(pairs, inter, dtype=dtype, device=DEVICE)
-    kernels.grouped_linear(x, gate_up, order, meta, top=top, by_token=True, max_tiles=max_tiles, pair_weight=weights.view(-1), out_act=act)
+    kernels.grouped_linear(x, gate_up, order, meta, top=top, by_token=True, max_tiles=max_tiles, pair_weight=weights.view(-1), out_act=act, wide=wide)
     each = torch.full((pairs, hidden), float("nan"), device=DEVICE)
-    kernels.grouped_linear(act, down, order, meta, top=top, by_token=False, max_tiles=max_tiles, out_y=each)
+    kernels.grouped_linear(act, down, order, meta, top=top, by_token=False, max_tiles=max_tiles, out_y=each, wide=wide)
     out = torch.empty(tokens, hidden, dtype=dtype, device=DEVICE)
     kernels.moe_combine(each, top, out, shared=shared, gate=gate)
     assert int(fault.item()) == 0
