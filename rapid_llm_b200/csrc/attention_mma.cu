@@ -66,7 +66,7 @@ struct AttentionArgs {
   int hq, hkv, page_size, num_pages, max_pages, slots, window, splits;
   float scale_log2;         // scale * log2(e)
   int* fault;
-  // Squashed scores and a sink (the mma.sync tiles and the merge kernel; the tcgen05 kernels take neither):
+  // Squashed scores and a sink (the mma.sync tiles, the merge kernel and the tcgen05 chunk tiles; not the tcgen05 decode tiles):
   // with softcap > 0 a score s becomes softcap * tanh(s / softcap) after the scale; with `sink` ([hq], float32)
   // every row's denominator also holds exp(sink[head]), a term without a key or a value, counted once.
   float scale;              // the plain scale (used with softcap)
@@ -340,8 +340,10 @@ attention_mma_kernel(const AttentionArgs args) {
           const bool keep = j <= row_pos[i] && j >= row_lo[i] && j < k_end;
           float v = -INFINITY;
           if (keep) {
+            // tanh by one exponential and one division: 1 - 2 / (1 + 2^(2 x log2 e)), exact at both ends
             v = args.softcap > 0.0f
-                    ? args.softcap * tanhf(s[nt][e] * args.scale / args.softcap) * 1.4426950408889634f
+                    ? args.softcap * 1.4426950408889634f *
+                          (1.0f - __fdividef(2.0f, 1.0f + exp2f(s[nt][e] * (2.8853900817779268f * args.scale / args.softcap))))
                     : s[nt][e] * args.scale_log2;
           }
           s[nt][e] = v;
@@ -574,6 +576,11 @@ static int launch_prefill_tc(const AttentionArgs& a, int n_items, bool pdl, cuda
   t.entry_slot = a.entry_slot; t.block_table = a.block_table; t.hq = a.hq; t.hkv = a.hkv;
   t.page_size = a.page_size; t.num_pages = a.num_pages; t.max_pages = a.max_pages; t.slots = a.slots;
   t.window = a.window; t.scale_log2 = a.scale_log2; t.fault = a.fault;
+  t.softcap = a.softcap; t.sink = a.sink; t.cap_in = 0.0f; t.cap_out = 0.0f;
+  if (a.softcap > 0.0f) {
+    t.cap_in = 2.0f * 1.4426950408889634f * a.scale / a.softcap;
+    t.cap_out = a.softcap * 1.4426950408889634f;
+  }
   return launch_kernel(attention_prefill_tc_kernel, dim3(a.hkv, n_items), dim3(kPfThreads), kPfSmemBytes, stream, pdl,
                        map, t);
 }
@@ -725,9 +732,8 @@ int rl_attention_mma(const void* q, const void* cache, void* out, float* part_ou
                      int chunk_rows, int decode_splits, float softcap, const float* sink, cudaStream_t stream) {
   if (tokens == 0 || (n_chunk_items == 0 && n_decode_items == 0)) return 0;
   const bool plain_scores = !(softcap > 0.0f) && sink == nullptr;
-  if (!plain_scores) {          // squashed scores and sinks run on the mma.sync tiles only
-    if (softcap < 0.0f || chunk_rows == attn::kPfRows || (decode_splits > 0 && decode_splits != splits))
-      return static_cast<int>(cudaErrorInvalidValue);
+  if (!plain_scores) {          // squashed scores and sinks: the tcgen05 chunk tiles and the mma.sync tiles take them
+    if (softcap < 0.0f || (decode_splits > 0 && decode_splits != splits)) return static_cast<int>(cudaErrorInvalidValue);
     decode_kernel = 1;
   }
   if (head_dim != attn::kD || hkv <= 0 || hq % hkv != 0 || page_size <= 0 || window < 0 ||

@@ -91,7 +91,18 @@ struct PrefillTcArgs {
   int hq, hkv, page_size, num_pages, max_pages, slots, window;
   float scale_log2;
   int* fault;
+  // Squashed scores (softcap > 0: a scaled score s becomes softcap * tanh(s / softcap)) and a sink ([hq] float32 or
+  // null: exp(sink[head]) joins every row's denominator once).  cap_in, cap_out: the squashed score in base-2 units is
+  // cap_out * (1 - 2 / (1 + 2^(raw * cap_in))), cap_in = 2 log2(e) scale / softcap, cap_out = softcap log2(e).
+  float softcap, cap_in, cap_out;
+  const float* sink;
 };
+
+__device__ __forceinline__ float pf_fast_rcp(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 __global__ void __launch_bounds__(kPfThreads, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const PrefillTcArgs args) {
@@ -352,6 +363,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const
     }
 
     const int my_blocks = tile_blocks[tile];
+    const bool capped = args.softcap > 0.0f;           // the same for every thread of the grid
+    const float post_scale = capped ? 1.0f : args.scale_log2;
     float ref_max = -INFINITY;                         // exponentials are taken against ref_max
     unsigned long long row_sum2 = pf_pack2(0.0f, 0.0f);   // the row's sum as two halves (even and odd keys)
     bool ok = true;
@@ -367,6 +380,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_load32(tmem_score(tile) + lane_bits + c * 32, score[c]);
       tmem_wait_ld();
+      if (capped) {
+        // tanh by one exponential and one reciprocal: 1 - 2 / (1 + 2^(2 x log2 e)); the results are in base-2 units
+        // already, so the scale below is one
+#pragma unroll
+        for (int i = 0; i < kPfKeys; ++i) {
+          const float raw = __uint_as_float(score[i >> 5][i & 31]);
+          const float squashed = fmaf(-2.0f * args.cap_out, pf_fast_rcp(1.0f + fast_exp2(raw * args.cap_in)), args.cap_out);
+          score[i >> 5][i & 31] = __float_as_uint(squashed);
+        }
+      }
       if (masked) {
 #pragma unroll
         for (int i = 0; i < kPfKeys; ++i) {
@@ -390,7 +413,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const
       for (int c = 0; c < 8; ++c) lane_max[c] = fmaxf(lane_max[c], __uint_as_float(score[3][24 + c]));
       float block_max = fmaxf(fmaxf(fmaxf(lane_max[0], lane_max[1]), fmaxf(lane_max[2], lane_max[3])),
                               fmaxf(fmaxf(lane_max[4], lane_max[5]), fmaxf(lane_max[6], lane_max[7])));
-      block_max *= args.scale_log2;                    // the scale is positive
+      block_max *= post_scale;                         // the scale is positive
       // The values product of the block before has added to O by now: products run in order, this
       // block's scores were issued after it, and the barrier that announced them counts everything
       // the issuing thread had issued before.  So O may be rescaled here without a further wait.
@@ -419,7 +442,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const
       const float shift = ref_max == -INFINITY ? 0.0f : ref_max;
       // P = 2^(s * scale - ref_max) as bfloat16, two per column, over S's columns; scale-and-shift and the sum
       // work on two keys an instruction
-      const unsigned long long scale2 = pf_pack2(args.scale_log2, args.scale_log2), shift2 = pf_pack2(-shift, -shift);
+      const unsigned long long scale2 = pf_pack2(post_scale, post_scale), shift2 = pf_pack2(-shift, -shift);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t packed[16];
@@ -448,7 +471,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const
       tc_fence_after();
       float even, odd;
       pf_unpack2(row_sum2, even, odd);
-      const float row_sum = even + odd;
+      float row_sum = even + odd;
+      if (args.sink != nullptr && valid) {
+        // the sink's term against the same reference point as the keys' (an infinite one: it alone counts, the row is zero)
+        const float sink2 = args.sink[kv_head * group + (p - token * group)] * 1.4426950408889634f;
+        row_sum += fast_exp2(sink2 - (ref_max == -INFINITY ? 0.0f : ref_max));
+      }
       const float inv = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {

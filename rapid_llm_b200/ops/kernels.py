@@ -531,8 +531,8 @@ def attention_mma(
     ``splits == 1``, where that kernel applies, up to 16.
 
     ``softcap`` > 0 squashes the scaled scores to ``softcap * tanh(s / softcap)``; ``sink`` (float32 ``[heads]``)
-    adds ``exp(sink[h])`` to every row's denominator, once.  Either one keeps the step on the mma.sync tiles
-    (``chunk_rows`` must then be :data:`CHUNK_TILE_ROWS`).
+    adds ``exp(sink[h])`` to every row's denominator, once.  The tcgen05 chunk tiles and the mma.sync tiles take
+    both; with either one the decode tiles run on mma.sync (and have no split count of their own).
     """
     _need_cuda(q, cache, out, chunk_items, decode_items, part_out, part_lse, cu_seqlens, entry_start,
                entry_slot, block_table, fault, sink)

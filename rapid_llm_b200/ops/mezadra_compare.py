@@ -138,7 +138,7 @@ def kernel_figures(width: int, hbm_gbs: float) -> dict:
         import numpy as np
 
         for capped in (True, False):
-            planner = AttentionItems(heads // kv_heads, kv_heads, d, tensor_core=not capped)
+            planner = AttentionItems(heads // kv_heads, kv_heads, d, decode_tensor_core=not capped)
             plan = planner.plan(StepShape(lengths=np.full(entries, per, dtype=np.int32), starts=np.full(entries, start, dtype=np.int32),
                                           decode_only=per == 1, page_size=page))
             chunk = torch.from_numpy(plan["chunk_items"]).to(device)
@@ -150,7 +150,7 @@ def kernel_figures(width: int, hbm_gbs: float) -> dict:
             attended = torch.empty_like(q)
             sink = f32(heads) if capped else None
             keys = sum(range(start + 1, start + per + 1)) * entries
-            label = "attention tiles, cap and sink (mma.sync)" if capped else "attention tiles, plain scores (tcgen05)"
+            label = "attention tiles, cap and sink" if capped else "attention tiles, plain scores"
             timed(label, tokens, entries, entries * (start + per) * kv_heads * d * 4 + tokens * heads * d * 4,
                   lambda: kernels.attention_mma(
                       q, cache, attended, chunk_items=chunk, decode_items=decode, splits=splits, part_out=part_out,

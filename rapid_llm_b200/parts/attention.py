@@ -80,16 +80,19 @@ class AttentionItems(StepPlanner):
     """
 
     def __init__(self, group: int, num_kv_heads: int, head_dim: int = 0, sms: int = DEFAULT_SMS,
-                 decode_clusters: dict[int, int] | None = None, tensor_core: bool = True) -> None:
+                 decode_clusters: dict[int, int] | None = None, tensor_core: bool = True,
+                 decode_tensor_core: bool = True) -> None:
         self.group, self.num_kv_heads, self.head_dim = int(group), int(num_kv_heads), int(head_dim)
-        # False: the mixer's scores are squashed or its softmax has a sink, which only the mma.sync tiles compute
+        # decode_tensor_core False: the mixer's scores are squashed or its softmax has a sink, which the tcgen05 chunk
+        # tiles and the mma.sync tiles compute, the tcgen05 decode tiles not; tensor_core False: mma.sync tiles only
         self.tensor_core = bool(tensor_core)
+        self.decode_tensor_core = self.tensor_core and bool(decode_tensor_core)
         self.decode_clusters = dict(decode_clusters or DEFAULT_DECODE_CLUSTERS)
         # work items the kernels want in flight: two CTAs per multiprocessor, one in a decode-only
         # step, whose kernel keeps a whole multiprocessor's shared memory busy
         self.target_ctas, self.decode_target_ctas = 2 * int(sms), int(sms)
         self.key = ("attention_items", self.group, self.num_kv_heads, self.head_dim, int(sms),
-                    tuple(sorted(self.decode_clusters.items())), self.tensor_core)
+                    tuple(sorted(self.decode_clusters.items())), self.tensor_core, self.decode_tensor_core)
 
     def capacity(self, max_tokens: int, max_entries: int) -> int:
         chunk_tiles = -(-max_tokens * self.group // kernels.CHUNK_TILE_ROWS) + max_entries
@@ -111,7 +114,7 @@ class AttentionItems(StepPlanner):
             if not shape.decode_only:
                 longest = int((starts + lengths).max())
                 splits = max(1, min(splits, longest // MIN_KEYS_PER_SPLIT))
-            elif tensor_core:
+            elif tensor_core and self.decode_tensor_core:
                 # ... and no more key ranges than the longest context has blocks of keys, rounded down to a power
                 # of two: a step's launch constants then change at a handful of context lengths only (the runner
                 # keeps a captured graph per set of constants)
@@ -137,7 +140,7 @@ class AttentionItems(StepPlanner):
         # their own (merged inside that kernel's clusters), or a request far into its context would be walked by one
         # CTA per kv head while the step waits.
         decode_splits = splits
-        if (tensor_core and not shape.decode_only and splits == 1 and chunk_rows == kernels.CHUNK_TILE_ROWS_TC
+        if (tensor_core and self.decode_tensor_core and not shape.decode_only and splits == 1 and chunk_rows == kernels.CHUNK_TILE_ROWS_TC
                 and bool(is_decode.any()) and not bool(is_decode.all())):
             decode_ctas = int(tiles[is_decode].sum()) * self.num_kv_heads
             blocks = max(1, -(-int((starts + lengths)[is_decode].max()) // kernels.DECODE_TC_KEYS))
@@ -240,7 +243,7 @@ class GQAAttention(Mixer):
             clusters = kernels.attention_decode_clusters(self.d, device) or None
         plain_scores = not self.softcap and not self.has_sink
         self._items = AttentionItems(self.hq // self.hkv, self.hkv, self.d, sms, clusters if plain_scores else None,
-                                     tensor_core=plain_scores)
+                                     decode_tensor_core=plain_scores)
         self.position = POSITION_ENCODINGS.build(position, dtype=dtype, device=device)
         self.rotary_dim = int(position.params.get("rotary_dim", getattr(self.position, "rotary_dim", self.d)))
 

@@ -111,6 +111,30 @@ def test_a_far_key_stands_out_among_hundreds(dtype, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES))
+def test_heads_of_128_on_the_tensor_core_tiles(dtype, tmp_path):
+    """Heads of 128 take the tcgen05 chunk tiles in bfloat16, where the cap and the sink are computed by other
+    instructions than in the other kernels: a low cap and large sinks, so that both decide the result; prompts long
+    enough for several blocks of keys, portions behind cached keys, single tokens beside them."""
+    config = make_config([
+        attention_layer(heads=4, kv_heads=2, dim=128, vdim=96, conv=3, rot_dims=32, scale=0.3, softcap=3.0, v_mix=True, mlp=dense()),
+        lightning_layer(heads=1, dim=128, vdim=128, decay=(0.97,), mlp=None),
+        attention_layer(heads=2, kv_heads=2, dim=128, vdim=96, conv=2, rot_dims=128, scale=0.1, softcap=25.0, v_mix=True, mlp=None),
+    ], width=128, vocab=150, scale=2.0)
+    weights = make_weights(config, seed=61)
+    weights["l0.mix.sink"] = torch.tensor([4.0, 0.5, -2.0, 7.0])
+    folder = write_folder(tmp_path / "model", config, weights, DTYPES[dtype])
+    sequences = _sequences(config, weights, [300, 45, 170], seed=5, dtype=dtype)
+    plain = {rid: forward(config, as_double(weights), tokens) for rid, tokens in sequences.items()}
+    runner = _runner(folder, config, dtype, 320, page=16)
+    tokens = sequences["r0"]
+    _compare(_replay(runner, whole("r0", tokens)), plain, dtype, f"heads of 128 {dtype} (whole)")
+    _compare(_replay(runner, portions("r0", tokens, [130, 2, 90, 1, 40])), plain, dtype, f"heads of 128 {dtype} (portions)")
+    _compare(_replay(runner, tail_one_by_one("r0", tokens, tail=12)), plain, dtype, f"heads of 128 {dtype} (tail)")
+    records, peak = mixed(sequences, seed=3, max_live=3, page=16)
+    _compare(_replay(_runner(folder, config, dtype, peak, page=16, slots=3), records), plain, dtype, f"heads of 128 {dtype} (mixed)")
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES))
 def test_the_first_tokens_of_a_sequence(dtype, tmp_path):
     """Positions 0 to 5 alone: the convolutions reach before the sequence's start (zeros, whatever the slot's tail
     held from its last owner), a position sees few keys and the sink weighs most.  Every slot is used twice."""
