@@ -589,7 +589,7 @@ def main() -> int:
                         "benchmark's; 14b and 32b are the other shapes of the same architecture")
     parser.add_argument("--context", type=int, default=CONTEXT, help="longest sequence the engine is set up for")
     parser.add_argument("--points", default="1,64", help="other batch sizes decoded beside --batch")
-    parser.add_argument("--sizes", default="2048,4096", help="widths of the models of --workload kopatar")
+    parser.add_argument("--sizes", default="2048,4096", help="widths of the models of --workload kopatar and --workload mezadra")
     parser.add_argument("--workload", choices=["decode", "serve", "kopatar", "mezadra"], default="decode", help="decode: the benchmark "
                         "(timed decode steps, a prefill, the points); serve: continuous batching of --requests "
                         "prompts of mixed lengths through generate()")
