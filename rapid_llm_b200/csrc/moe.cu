@@ -32,11 +32,12 @@ constexpr int kMoeStages = 3;
 __device__ __forceinline__ float moe_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
 
 // ------------------------------------------------------------------ router
-// One block per kRouterTokens tokens; a warp takes rows e = warp, warp + warps, ... of W_r and forms the row's
-// product with each of the block's tokens at once (the row is read once for all of them).  A product's sum
-// runs over k = lane, lane + 32, ... and then down the warp's tree, whatever else is in the block, so a token's
-// logits do not depend on the batch.  The logits meet in shared memory ([tokens][E + G]); warp t then picks
-// token t's experts.
+// One block per kRouterTokens tokens.  The block's warps share the inner range: warp w forms, for every router row
+// and each of the block's tokens, the part of the product over its slice of k (the row's slice is read once for all
+// the tokens; 16-byte loads where sizes and addresses allow), so a step's loads are all in flight at once instead
+// of one row after the other.  The parts meet in shared memory and are added in the order of the warps.  A token's
+// logits thus have a fixed order of sums, whatever else is in the block or the step.  Warp t then picks token t's
+// experts.
 constexpr int kRouterTokens = 4;
 constexpr int kRouterWarps = 8;
 
@@ -56,50 +57,80 @@ __global__ void __launch_bounds__(kRouterWarps * 32)
 router_topk_kernel(const T* x, int x_stride, const float* __restrict__ w, int hidden, int experts,
                    int gates, int top, int* __restrict__ ids, float* __restrict__ weights,
                    float* __restrict__ gate_out, float* __restrict__ scores_out, int tokens, int wide) {
-  extern __shared__ float moe_scores[];      // [kRouterTokens][experts + gates]
+  extern __shared__ float moe_scores[];      // [kRouterTokens][rows] logits, then [kRouterWarps][kRouterTokens][rows] parts
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t0 = blockIdx.x * kRouterTokens;
   const int rows = experts + gates;
+  float* parts = moe_scores + kRouterTokens * rows;
+  // the warp's slice of k: whole steps of 128, so that a lane's four neighbours stay together
+  const int steps = (hidden + 127) / 128, per_warp = (steps + kRouterWarps - 1) / kRouterWarps;
+  const int k_begin = min(hidden, warp * per_warp * 128), k_end = min(hidden, (warp + 1) * per_warp * 128);
   pdl_wait();
   const T* xr[kRouterTokens];
 #pragma unroll
   for (int i = 0; i < kRouterTokens; ++i)
     xr[i] = x + static_cast<size_t>(min(t0 + i, tokens - 1)) * x_stride;      // rows past the end repeat the last one
-  for (int e = warp; e < rows; e += kRouterWarps) {
-    const float* wr = w + static_cast<size_t>(e) * hidden;
-    float acc[kRouterTokens];
+  if (wide) {
+    // eight router rows at a time: their loads leave together (a row after the other would wait for memory once per row)
+    constexpr int kRowsAtOnce = 8;
+    for (int e0 = 0; e0 < rows; e0 += kRowsAtOnce) {
+      float acc[kRowsAtOnce][kRouterTokens];
 #pragma unroll
-    for (int i = 0; i < kRouterTokens; ++i) acc[i] = 0.0f;
-    if (wide) {
-      // four neighbouring k a lane and step (16- and 8-byte loads), eight steps in flight
-#pragma unroll 8
-      for (int k = lane * 4; k < hidden; k += 128) {
-        const float4 wv = *reinterpret_cast<const float4*>(wr + k);
+      for (int j = 0; j < kRowsAtOnce; ++j)
+#pragma unroll
+        for (int i = 0; i < kRouterTokens; ++i) acc[j][i] = 0.0f;
+      for (int k = k_begin + lane * 4; k < k_end; k += 128) {
+        float4 wv[kRowsAtOnce];
+#pragma unroll
+        for (int j = 0; j < kRowsAtOnce; ++j)
+          wv[j] = *reinterpret_cast<const float4*>(w + static_cast<size_t>(min(e0 + j, rows - 1)) * hidden + k);
+        float xv[kRouterTokens][4];
+#pragma unroll
+        for (int i = 0; i < kRouterTokens; ++i) router_load4(xr[i] + k, xv[i]);
+#pragma unroll
+        for (int j = 0; j < kRowsAtOnce; ++j)
+#pragma unroll
+          for (int i = 0; i < kRouterTokens; ++i) {
+            acc[j][i] = fmaf(wv[j].x, xv[i][0], acc[j][i]);
+            acc[j][i] = fmaf(wv[j].y, xv[i][1], acc[j][i]);
+            acc[j][i] = fmaf(wv[j].z, xv[i][2], acc[j][i]);
+            acc[j][i] = fmaf(wv[j].w, xv[i][3], acc[j][i]);
+          }
+      }
+#pragma unroll
+      for (int j = 0; j < kRowsAtOnce; ++j)
 #pragma unroll
         for (int i = 0; i < kRouterTokens; ++i) {
-          float xv[4];
-          router_load4(xr[i] + k, xv);
-          acc[i] = fmaf(wv.x, xv[0], acc[i]);
-          acc[i] = fmaf(wv.y, xv[1], acc[i]);
-          acc[i] = fmaf(wv.z, xv[2], acc[i]);
-          acc[i] = fmaf(wv.w, xv[3], acc[i]);
+          const float total = warp_sum(acc[j][i]);
+          if (lane == 0 && e0 + j < rows) parts[(warp * kRouterTokens + i) * rows + e0 + j] = total;
         }
-      }
-    } else {
-#pragma unroll 4
-      for (int k = lane; k < hidden; k += 32) {
+    }
+  } else {
+    for (int e = 0; e < rows; ++e) {
+      const float* wr = w + static_cast<size_t>(e) * hidden;
+      float acc[kRouterTokens];
+#pragma unroll
+      for (int i = 0; i < kRouterTokens; ++i) acc[i] = 0.0f;
+      for (int k = k_begin + lane; k < k_end; k += 32) {
         const float wv = wr[k];
 #pragma unroll
         for (int i = 0; i < kRouterTokens; ++i) acc[i] = fmaf(wv, to_float(xr[i][k]), acc[i]);
       }
-    }
 #pragma unroll
-    for (int i = 0; i < kRouterTokens; ++i) {
-      const float total = warp_sum(acc[i]);
-      // the logit: the choice is made on it (sigmoid keeps the order, and does not saturate into ties)
-      if (lane == 0) moe_scores[i * rows + e] = total;
+      for (int i = 0; i < kRouterTokens; ++i) {
+        const float total = warp_sum(acc[i]);
+        if (lane == 0) parts[(warp * kRouterTokens + i) * rows + e] = total;
+      }
     }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < kRouterTokens * rows; idx += blockDim.x) {
+    float total = 0.0f;
+#pragma unroll
+    for (int part = 0; part < kRouterWarps; ++part) total += parts[part * kRouterTokens * rows + idx];
+    // the logit: the choice is made on it (sigmoid keeps the order, and does not saturate into ties)
+    moe_scores[idx] = total;
   }
   __syncthreads();
   if (warp >= kRouterTokens || t0 + warp >= tokens) return;
@@ -583,12 +614,17 @@ int rl_router_topk(int dtype, const void* x, int x_stride, const float* w, int h
   if (tokens == 0) return 0;
   if (experts < 1 || top < 1 || top > experts || gates < 0 || (gates > 0 && gate_out == nullptr) || hidden < 1)
     return static_cast<int>(cudaErrorInvalidValue);
-  const size_t smem = static_cast<size_t>(rl::kRouterTokens) * (experts + gates) * sizeof(float);
-  if (smem > 48 * 1024) return static_cast<int>(cudaErrorInvalidValue);
+  const size_t smem = static_cast<size_t>(rl::kRouterTokens) * (rl::kRouterWarps + 1) * (experts + gates) * sizeof(float);
+  if (smem > 200 * 1024) return static_cast<int>(cudaErrorInvalidValue);
   // whole rows in 16-byte pieces: which order a row's sum runs in depends on the sizes and addresses alone
   const int wide = hidden % 4 == 0 && x_stride % 4 == 0 &&
                    ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
   RL_DISPATCH_DTYPE(dtype, {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(rl::router_topk_kernel<scalar_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(smem));
+      if (e != cudaSuccess) return static_cast<int>(e);
+    }
     return rl::launch_kernel(rl::router_topk_kernel<scalar_t>,
                              dim3((tokens + rl::kRouterTokens - 1) / rl::kRouterTokens), dim3(rl::kRouterWarps * 32),
                              smem, stream, pdl != 0, static_cast<const scalar_t*>(x), x_stride, w, hidden, experts,

@@ -954,7 +954,9 @@ int rl_gated_norm(int dtype, int y_f32, const void* y, int y_stride, const void*
   int threads = 32;
   while (threads < 256 && threads * 2 <= group) threads *= 2;
   const dim3 grid(tokens, groups), block(threads);
-  if (group % 4 == 0 && group <= 2048) {
+  // a warp per (token, group) while a group is a warp's work; a group of thousands of columns (one norm over all
+  // heads) takes a block, or the few warps of a small step would each walk it alone
+  if (group % 4 == 0 && group <= 512) {
     const long long total = static_cast<long long>(tokens) * groups;
     const dim3 warp_grid(static_cast<unsigned>((total + 7) / 8)), warp_block(256);
     const bool wide = ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
