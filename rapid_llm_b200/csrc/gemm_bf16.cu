@@ -72,10 +72,22 @@ struct GemmArgs {
   // added to every row of the result (after the open scale, before the SiLU or the residual add);
   // [N], for SwiGLU [2 N] with the gate's part first; may be null
   const float* bias;
+  // the gated unit of a fused gate/up product: glu_limit == 0: silu(gate) * up; glu_limit > 0: the clamped unit
+  // g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(glu_alpha * g) * (u + 1)
+  float glu_limit, glu_alpha;
 };
 
 __device__ __forceinline__ float silu_mul(float gate, float up) {
   return __fdividef(gate, 1.0f + __expf(-gate)) * up;   // the result is rounded to bfloat16
+}
+
+__device__ __forceinline__ float gated_unit(float gate, float up, float limit, float alpha) {
+  if (limit > 0.0f) {      // the same branch for every thread of the grid
+    gate = fminf(gate, limit);
+    up = fminf(fmaxf(up, -limit), limit);
+    return __fdividef(gate, 1.0f + __expf(-alpha * gate)) * (up + 1.0f);
+  }
+  return silu_mul(gate, up);
 }
 
 // One element of a product that a norm follows: the residual takes the sum, the output the sum times
@@ -324,7 +336,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             float u[16];
             tmem_load16(acc + BN + c, u);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = silu_mul(v[j], (scaled ? u[j] * row_scale[c + j] : u[j]) + bias_up);
+            for (int j = 0; j < 16; ++j) v[j] = gated_unit(v[j], (scaled ? u[j] * row_scale[c + j] : u[j]) + bias_up, args.glu_limit, args.glu_alpha);
           }
           if (!kSwiglu && args.residual != nullptr) {
             const float norm_w = n < args.N ? args.norm_weight[n] : 0.0f;
@@ -416,7 +428,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
           const float g = gate[r] * scale + bias_gate[r], u = up[r] * scale + bias_up[r];
-          result[r] = kSwiglu ? silu_mul(g, u) : g;
+          result[r] = kSwiglu ? gated_unit(g, u, args.glu_limit, args.glu_alpha) : g;
         }
         if (norm_follows) {
           float before[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -563,11 +575,13 @@ extern "C" {
 // A norm that came before (`sumsq_in[tokens, sumsq_count]`, at most 64 tokens): row t of the result is
 // multiplied by rsqrt(sum(sumsq_in[t]) / norm_size + norm_eps).
 // `bias` (float32 [n_out], SwiGLU [2 n_out]; may be null) is added to every row after that scale.
+// `glu_limit` > 0 (only with swiglu): the gated unit is the clamped one, see GemmArgs.
 int rl_gemm_bf16_norm(const void* x, const void* w, void* out, int tokens, int n_out, int k, int swiglu, int pdl,
                       int k_split, float* residual, const float* norm_weight, float* sumsq_out,
                       const float* sumsq_in, int sumsq_count, float norm_eps, int norm_size, const float* bias,
-                      int* fault, cudaStream_t stream) {
+                      float glu_limit, float glu_alpha, int* fault, cudaStream_t stream) {
   if (tokens == 0 || n_out == 0) return 0;
+  if (glu_limit < 0.0f || (glu_limit > 0.0f && swiglu == 0)) return static_cast<int>(cudaErrorInvalidValue);
   if (tokens < 0 || n_out < 0 || k <= 0 || k % 8 != 0 || k_split < 0 || k_split > 8 ||
       (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
     return static_cast<int>(cudaErrorInvalidValue);
@@ -619,6 +633,7 @@ int rl_gemm_bf16_norm(const void* x, const void* w, void* out, int tokens, int n
   args.norm_eps = norm_eps;
   args.inv_norm_size = norm_size > 0 ? 1.0f / static_cast<float>(norm_size) : 0.0f;
   args.bias = bias;
+  args.glu_limit = glu_limit; args.glu_alpha = glu_alpha;
 #define RL_GEMM_CASE(SW, BNV) \
   if ((swiglu != 0) == SW && bn == BNV) return rl::launch_gemm<SW, BNV>(map_w, map_x, args, k_split, stream);
   RL_GEMM_CASE(false, 16) RL_GEMM_CASE(false, 32) RL_GEMM_CASE(false, 64) RL_GEMM_CASE(false, 128)
@@ -631,7 +646,7 @@ int rl_gemm_bf16_norm(const void* x, const void* w, void* out, int tokens, int n
 int rl_gemm_bf16(const void* x, const void* w, void* out, int tokens, int n_out, int k, int swiglu, int pdl,
                  int k_split, int* fault, cudaStream_t stream) {
   return rl_gemm_bf16_norm(x, w, out, tokens, n_out, k, swiglu, pdl, k_split, nullptr, nullptr, nullptr, nullptr, 0,
-                           0.0f, 0, nullptr, fault, stream);
+                           0.0f, 0, nullptr, 0.0f, 0.0f, fault, stream);
 }
 
 // columns of the table of partial sums of squares that a product of `n_out` output columns writes per token

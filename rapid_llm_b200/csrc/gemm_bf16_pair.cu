@@ -72,6 +72,7 @@ struct PairArgs {
   int out_cols;            // columns of the result per tile: 256, SwiGLU 128
   int pdl;
   const float* bias;       // [N] (SwiGLU: [2 N]) or null
+  float glu_limit, glu_alpha;   // glu_limit > 0: the clamped unit min(g, l) * sigmoid(alpha g) * (clamp(u, +-l) + 1) instead of SiLU(g) * u
   // a norm that came before and left its scale open: row t is multiplied by rsqrt(sum(sumsq_in[t, :]) * inv + eps)
   const float* sumsq_in;
   int sumsq_count;
@@ -180,6 +181,14 @@ __device__ __forceinline__ unsigned pair_load_acquire(const unsigned* p) {
 }
 
 __device__ __forceinline__ float pair_silu_mul(float gate, float up) { return __fdividef(gate, 1.0f + __expf(-gate)) * up; }
+__device__ __forceinline__ float pair_gated_unit(float gate, float up, float limit, float alpha) {
+  if (limit > 0.0f) {      // the same branch for every thread of the grid
+    gate = fminf(gate, limit);
+    up = fminf(fmaxf(up, -limit), limit);
+    return __fdividef(gate, 1.0f + __expf(-alpha * gate)) * (up + 1.0f);
+  }
+  return pair_silu_mul(gate, up);
+}
 
 template <bool kSwiglu>
 __global__ void __launch_bounds__(kPairThreads, 1)
@@ -465,7 +474,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             float value = v[j] * scale + (args.bias != nullptr && inside ? __ldg(args.bias + n) : 0.0f);
             if (kSwiglu) {
               const float up = u[j] * scale + (args.bias != nullptr && inside ? __ldg(args.bias + args.N + n) : 0.0f);
-              value = pair_silu_mul(value, up);
+              value = pair_gated_unit(value, up, args.glu_limit, args.glu_alpha);
             }
             v[j] = value;
           }
@@ -610,8 +619,10 @@ int rl_gemm_bf16_pair_counter_words() { return 2 * rl::kPairMaxTiles; }
 int rl_gemm_bf16_pair(const void* x, const void* w, void* out, int tokens, int n_out, int k, int swiglu, int pdl,
                       float* residual, const float* norm_weight, float* sumsq_out, int sumsq_out_count,
                       const float* sumsq_in, int sumsq_count, float norm_eps, int norm_size, const float* bias,
-                      float* scratch, unsigned* counters, int* fault, cudaStream_t stream) {
+                      float glu_limit, float glu_alpha, float* scratch, unsigned* counters, int* fault,
+                      cudaStream_t stream) {
   if (tokens == 0 || n_out == 0) return 0;
+  if (glu_limit < 0.0f || (glu_limit > 0.0f && swiglu == 0)) return static_cast<int>(cudaErrorInvalidValue);
   if (tokens < 0 || n_out < 0 || n_out % 8 != 0 || k <= 0 || k % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) ||
       (reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) ||
       (reinterpret_cast<uintptr_t>(residual) & 15) || (reinterpret_cast<uintptr_t>(norm_weight) & 15) ||
@@ -629,6 +640,7 @@ int rl_gemm_bf16_pair(const void* x, const void* w, void* out, int tokens, int n
   args.k_blocks = (k + rl::kPairTileK - 1) / rl::kPairTileK;
   args.pdl = pdl;
   args.bias = bias;
+  args.glu_limit = glu_limit; args.glu_alpha = glu_alpha;
   args.sumsq_in = sumsq_in; args.sumsq_count = sumsq_count; args.norm_eps = norm_eps;
   args.inv_norm_size = norm_size > 0 ? 1.0f / static_cast<float>(norm_size) : 0.0f;
   args.residual = residual; args.norm_weight = norm_weight; args.sumsq_out = sumsq_out; args.sumsq_out_count = sumsq_out_count;

@@ -178,22 +178,27 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, fault: torch.Tensor | Non
 
 
 def gated_linear(x, gate_up: torch.Tensor, act: torch.Tensor, workspace, fault: torch.Tensor, *,
-                 defer: bool = False) -> torch.Tensor:
-    """``act = silu(x @ gate^T) * (x @ up^T)`` for a ``[2 I, K]`` weight with the gate rows first.
+                 defer: bool = False, clamp: tuple[float, float] | None = None) -> torch.Tensor:
+    """``act = silu(x @ gate^T) * (x @ up^T)`` for a ``[2 I, K]`` weight with the gate rows first; with
+    ``clamp = (limit, alpha)`` the clamped unit ``g * sigmoid(alpha g) * (u + 1)``, ``g = min(gate, limit)``,
+    ``u = clamp(up, -limit, limit)``.
 
     One fused tensor-core kernel where it applies; otherwise the product into a ``[T, 2 I]``
-    buffer from ``workspace`` followed by the SiLU-multiply kernel.  ``x`` may be :class:`ScaledRows`.
+    buffer from ``workspace`` followed by the activation's kernel.  ``x`` may be :class:`ScaledRows`.
     """
     x, scale = _open_scale(x)
+    unit = {} if clamp is None else {"glu_limit": float(clamp[0]), "glu_alpha": float(clamp[1])}
     if use_tensor_core_kernel(x, gate_up):
-        _product(x, gate_up, act, fault, defer, swiglu=True, **scale)
+        _product(x, gate_up, act, fault, defer and clamp is None, swiglu=True, **scale, **unit)
         return act
     if scale:
         raise kernels.KernelError("gated_linear: rows with an open scale need the tensor-core product")
     if (x.dtype == torch.bfloat16 and x.shape[0] >= PAIR_GATED_MIN_TOKENS and FORCE in (None, "pair")
             and kernels.gemm_bf16_supports(x, gate_up) and kernels.gemm_bf16_pair_takes(x.shape[0], act.shape[1], True)):
         flush()
-        return kernels.gemm_bf16_pair(x, gate_up, act, fault, swiglu=True)      # no [T, 2 I] intermediate
+        return kernels.gemm_bf16_pair(x, gate_up, act, fault, swiglu=True, **unit)      # no [T, 2 I] intermediate
     wide = workspace.get("ffn_gate_up", x.shape[0], gate_up.shape[0], x.dtype)
     linear(x, gate_up, wide, fault)
+    if clamp is not None:
+        return kernels.clamped_glu(wide, act, clamp[0], clamp[1])
     return kernels.silu_mul(wide, act)

@@ -604,7 +604,7 @@ def gemm_lib() -> ctypes.CDLL:
         lib.rl_gemm_bf16.restype = c_int
         lib.rl_gemm_bf16_norm.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                           c_void_p, c_void_p, c_void_p, c_void_p, c_int, ctypes.c_float, c_int,
-                                          c_void_p, c_void_p, c_void_p]
+                                          c_void_p, c_float, c_float, c_void_p, c_void_p]
         lib.rl_gemm_bf16_norm.restype = c_int
         lib.rl_gemm_bf16_sumsq_count.argtypes = [c_int]
         lib.rl_gemm_bf16_sumsq_count.restype = c_int
@@ -628,11 +628,14 @@ def gemm_bf16_sumsq_count(n_out: int) -> int:
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, fault: torch.Tensor, *, swiglu: bool = False,
               k_split: int = 0, residual: torch.Tensor | None = None, norm_weight: torch.Tensor | None = None,
               sumsq_out: torch.Tensor | None = None, sumsq_in: torch.Tensor | None = None,
-              norm_eps: float = 0.0, norm_size: int = 0, bias: torch.Tensor | None = None) -> torch.Tensor:
+              norm_eps: float = 0.0, norm_size: int = 0, bias: torch.Tensor | None = None,
+              glu_limit: float = 0.0, glu_alpha: float = 1.0) -> torch.Tensor:
     """``out[T, N] = x[T, K] @ w[N, K]^T`` in bfloat16 on the tcgen05 tensor cores.
 
     With ``swiglu``, ``w`` is ``[2 N, K]`` (gate rows, then up rows) and
-    ``out = silu(x @ gate^T) * (x @ up^T)`` without the ``[T, 2 N]`` intermediate.
+    ``out = silu(x @ gate^T) * (x @ up^T)`` without the ``[T, 2 N]`` intermediate; with ``glu_limit`` > 0 the unit
+    is the clamped one instead, ``g * sigmoid(glu_alpha g) * (u + 1)`` with ``g = min(gate, limit)``,
+    ``u = clamp(up, -limit, limit)``.
     ``k_split`` forces how many CTAs share a tile's inner range (0 = the kernel chooses).
 
     A norm between two products rides on them (at most :data:`GEMM_NORM_MAX_TOKENS` rows).
@@ -679,7 +682,7 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, fault: torch.
             _ptr(x), _ptr(w), _ptr(out), tokens, n_out, k, int(swiglu), int(PDL), int(k_split),
             _ptr(residual), _ptr(norm_weight), _ptr(sumsq_out),
             _ptr(sumsq_in), 0 if sumsq_in is None else sumsq_in.shape[1], float(norm_eps), int(norm_size),
-            _ptr(bias), _ptr(fault), _stream(),
+            _ptr(bias), float(glu_limit), float(glu_alpha), _ptr(fault), _stream(),
         ),
         f"gemm_bf16({tokens}x{k} by {n_out})",
     )
@@ -690,7 +693,7 @@ def gemm_bf16_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, fault: t
                    bias: torch.Tensor | None = None, *, swiglu: bool = False,
                    residual: torch.Tensor | None = None, norm_weight: torch.Tensor | None = None,
                    sumsq_out: torch.Tensor | None = None, sumsq_in: torch.Tensor | None = None,
-                   norm_eps: float = 0.0, norm_size: int = 0) -> torch.Tensor:
+                   norm_eps: float = 0.0, norm_size: int = 0, glu_limit: float = 0.0, glu_alpha: float = 1.0) -> torch.Tensor:
     """``out[T, N] = x[T, K] @ w[N, K]^T (+ bias)`` in bfloat16 for steps of many tokens: pairs of CTAs on
     256 x 256 tiles (``tcgen05.mma.cta_group::2``), persistent over the tiles, the tokens on the accumulator's lanes.
 
@@ -730,7 +733,7 @@ def gemm_bf16_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, fault: t
     if not getattr(lib, "_pair_declared", False):
         lib.rl_gemm_bf16_pair.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                           c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_float, c_int, c_void_p,
-                                          c_void_p, c_void_p, c_void_p, c_void_p]
+                                          c_float, c_float, c_void_p, c_void_p, c_void_p, c_void_p]
         lib.rl_gemm_bf16_pair.restype = c_int
         lib.rl_gemm_bf16_pair_scratch_floats.restype = c_longlong
         lib.rl_gemm_bf16_pair_counter_words.restype = c_int
@@ -744,7 +747,8 @@ def gemm_bf16_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, fault: t
                                  _ptr(residual), _ptr(norm_weight), _ptr(sumsq_out),
                                  0 if sumsq_out is None else sumsq_out.shape[1],
                                  _ptr(sumsq_in), 0 if sumsq_in is None else sumsq_in.shape[1], float(norm_eps), int(norm_size),
-                                 _ptr(bias), _ptr(state[0]), _ptr(state[1]), _ptr(fault), _stream()),
+                                 _ptr(bias), float(glu_limit), float(glu_alpha), _ptr(state[0]), _ptr(state[1]), _ptr(fault),
+                                 _stream()),
            f"gemm_bf16_pair({tokens}x{k} by {n_out})")
     return out
 

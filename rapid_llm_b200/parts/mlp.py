@@ -68,7 +68,8 @@ class SwiGLU(FeedForward):
 class ClampedGLU(SwiGLU):
     """``down(g * sigmoid(alpha g) * (u + 1))`` with ``g = min(gate(x), limit)`` and ``u = clamp(up(x), -limit, limit)``:
     a gated unit whose branches are bounded before they meet, the linear branch shifted by one.  Gate and up
-    share one product as in :class:`SwiGLU`; the activation is float32 arithmetic on the product's result."""
+    share one product as in :class:`SwiGLU`, and the unit rides in its epilogue where :class:`SwiGLU`'s does (float32
+    arithmetic on the accumulators); elsewhere it is a kernel on the product's result."""
 
     rides_norms = False
 
@@ -80,9 +81,8 @@ class ClampedGLU(SwiGLU):
 
     def forward(self, x, batch):
         rows = x.shape[0]
-        wide = batch.workspace.get("ffn_gate_up", rows, 2 * self.inter, x.dtype)
-        gemm.linear(x, self.gate_up, wide, batch.fault)
-        act = kernels.clamped_glu(wide, batch.workspace.get("ffn_act", rows, self.inter, x.dtype), self.limit, self.alpha)
+        act = batch.workspace.get("ffn_act", rows, self.inter, x.dtype)
+        gemm.gated_linear(x, self.gate_up, act, batch.workspace, batch.fault, clamp=(self.limit, self.alpha))
         return gemm.linear(act, self.down, batch.workspace.get("ffn_out", rows, self.hidden, x.dtype), batch.fault)
 
 

@@ -144,3 +144,25 @@ def test_the_clamped_gated_unit_and_the_scaled_embedding(dtype):
     fault = torch.zeros(1, dtype=torch.int32, device=DEVICE)
     kernels.embedding(rows, table, ids, fault, scale=13.5, stream=stream)
     assert torch.equal(stream, table[ids.long()].float() * 13.5) and torch.equal(rows, stream.to(dtype)) and int(fault.item()) == 0
+
+
+@pytest.mark.parametrize("tokens", [5, 64, 300, 1100])
+def test_the_clamped_unit_rides_on_the_gate_up_product(tokens):
+    """Small steps: the streaming tcgen05 product's epilogue; a thousand tokens and more: the pair kernel's; between
+    them the library product and the unit's own kernel.  All against float32 arithmetic on the same bfloat16 operands."""
+    from rapid_llm_b200.engine.batch import Workspace
+    from rapid_llm_b200.ops import gemm
+
+    g = torch.Generator().manual_seed(tokens)
+    hidden, inter, limit, alpha = 256, 384, 0.8, 1.702
+    x = torch.randn(tokens, hidden, generator=g).to(torch.bfloat16).to(DEVICE)
+    w = (2 * torch.randn(2 * inter, hidden, generator=g) / hidden ** 0.5).to(torch.bfloat16).to(DEVICE)
+    fault = torch.zeros(1, dtype=torch.int32, device=DEVICE)
+    act = torch.empty(tokens, inter, dtype=torch.bfloat16, device=DEVICE)
+    gemm.gated_linear(x, w, act, Workspace(tokens, torch.device(DEVICE)), fault, clamp=(limit, alpha))
+    wide = x.float() @ w.float().T
+    gate, up = wide[:, :inter].clamp(max=limit), wide[:, inter:].clamp(-limit, limit)
+    want = gate * torch.sigmoid(alpha * gate) * (up + 1)
+    assert int(fault.item()) == 0
+    assert float((gate == limit).float().mean()) > 0.05 and float((up.abs() == limit).float().mean()) > 0.05      # the limits bite
+    torch.testing.assert_close(act.float(), want, rtol=2e-2, atol=2e-2)
