@@ -7,7 +7,7 @@ the kernels that came with the design alone against their rooflines.
 
 Random weights, bfloat16, one GPU.  A model of width ``W`` has six layers, ``lightning, attention, lightning,
 lightning, attention, lightning`` with the feed-forwards ``dense, experts, dense, experts, dense, experts``: heads of
-128 (attention: values of 64, a kv head per four heads, four taps, 64 rotated entries, a cap of 50), a dense
+128 (attention: a kv head per four heads, four taps, 32 rotated entries, a cap of 30), a dense
 feed-forward of ``8 W / 3`` (rounded to 256), 16 experts of ``W / 4`` of which a token takes two, and a shared expert
 of ``W / 2``.  The Qwen3 beside it has six layers.  Prefill is one 2,048-token step (best of three, CUDA events around
 the step function); decode is batch 8 behind 1,024-token prompts, replayed from the captured graph (median of 32
@@ -34,8 +34,8 @@ def mezadra_raw(width: int) -> dict:
     heads = width // 128
     lightning = {"heads": heads, "dim": 128, "vdim": 128,
                  "decay": [1.0 - 2.0 ** (-3 - 7 * h / max(heads - 1, 1)) for h in range(heads)]}
-    attention = {"heads": heads, "kv_heads": max(heads // 4, 1), "dim": 128, "vdim": 64, "conv": 4,
-                 "rot": {"dims": 64, "base": 50000.0}, "scale": 128 ** -0.5, "softcap": 50.0, "v_mix": True}
+    attention = {"heads": heads, "kv_heads": max(heads // 4, 1), "dim": 128, "vdim": 128, "conv": 4,
+                 "rot": {"dims": 32, "base": 1.0e6}, "scale": 128 ** -0.5, "softcap": 30.0, "v_mix": True}
     dense = {"kind": "dense", "ff": (8 * width // 3 + 255) // 256 * 256, "limit": 7.0}
     experts = {"kind": "moe", "router": {"experts": EXPERTS, "top": TOP}, "expert": {"ff": width // 4},
                "shared": {"ff": width // 2}}
@@ -128,7 +128,7 @@ def kernel_figures(width: int, hbm_gbs: float) -> dict:
         slot_of = torch.arange(entries, dtype=torch.int32, device=device).repeat_interleave(per)
         dest = (table[slot_of.long(), (positions // page).long()] * page + positions % page).to(torch.int32)
         q = torch.empty(tokens, heads * d, dtype=torch.bfloat16, device=device)
-        inv_freq, mix, first = torch.rand(32, device=device), torch.rand(1, device=device), f32(tokens, kv_heads * d)
+        inv_freq, mix, first = torch.rand(16, device=device), torch.rand(1, device=device), f32(tokens, kv_heads * d)
         timed("rope_unit_write", tokens, entries, tokens * channels * 6 + tokens * kv_heads * d * 4,
               lambda: kernels.rope_unit_write(conv, q, num_heads=heads, num_kv_heads=kv_heads, head_dim=d, inv_freq=inv_freq,
                                               positions=positions, kv_dest=dest, cache=cache, page_size=page, norm_size=d,
@@ -157,7 +157,7 @@ def kernel_figures(width: int, hbm_gbs: float) -> dict:
                       part_lse=part_lse, cu_seqlens=batch.cu_seqlens, entry_start=batch.entry_start, entry_slot=batch.entry_slot,
                       block_table=table, num_heads=heads, num_kv_heads=kv_heads, head_dim=d, window=0, scale=d ** -0.5,
                       fault=fault, decode_rows=plan["decode_rows"], chunk_rows=plan["chunk_rows"],
-                      decode_splits=plan["decode_splits"], softcap=50.0 if capped else 0.0, sink=sink),
+                      decode_splits=plan["decode_splits"], softcap=30.0 if capped else 0.0, sink=sink),
                   flops=4.0 * keys * heads * d)
     assert int(fault.item()) == 0, "a kernel reported a fault"
     return out
