@@ -140,7 +140,9 @@ def routed_experts(h: torch.Tensor, w: dict, prefix: str, mlp: dict, margins: li
     if margins is not None and top < scores.shape[1]:
         logits = torch.sort(h @ w[prefix + "router"].T, dim=-1, descending=True).values
         margins.extend(((logits[:, top - 1] - logits[:, top]) / (logits.std(-1) + 1e-9)).tolist())
-    chosen = torch.topk(scores, top, dim=-1).indices
+    # the largest scores are the largest logits; choosing on the logits keeps large ones apart that the sigmoid,
+    # in any float format, rounds to the same 1.0
+    chosen = torch.topk(h @ w[prefix + "router"].T, top, dim=-1).indices
     out = torch.zeros(h.shape[0], w[prefix + "e0.down"].shape[0], dtype=F)
     for t in range(h.shape[0]):
         for e in chosen[t].tolist():
