@@ -3,8 +3,9 @@
 //
 // A step's T tokens each choose `top` of E experts; pair i = t * top + j is token t's j-th choice.
 //   rl_router_topk    z = W_r h in float32 (W_r float32, h the engine's dtype), s = sigmoid(z), the
-//                     `top` largest s per token (ties: the lower index) with their s as weights; extra
-//                     rows of W_r behind the experts' give sigmoid gates per token (a shared expert's).
+//                     `top` largest per token, chosen on z (sigmoid keeps the order; ties: the lower
+//                     index) with their s as weights; extra rows of W_r behind the experts' give
+//                     sigmoid gates per token (a shared expert's).
 //   rl_moe_plan       counts the pairs per expert and lays them out expert by expert in tiles of
 //                     kTileM rows: sorted[p] = i, tile tables, all on the device (no host round trip).
 //   rl_grouped_linear out rows = A rows @ W[e]^T over the tiles; A rows are fetched by token
@@ -15,8 +16,10 @@
 // A row's result does not depend on its tile's other rows or on the order in which the pairs of an
 // expert were laid out: the inner sums run over k in a fixed order per row.
 //
-// Two product kernels: float32 FMA tiles (the 32-bit engine; any sizes) and mma.sync m16n8k16 tiles
-// for bfloat16 (float32 accumulators).
+// Three product kernels: float32 FMA tiles (the 32-bit engine; any sizes), mma.sync m16n8k16 tiles for
+// bfloat16 (float32 accumulators; any sizes), and the same instruction behind a cp.async ring with
+// ldmatrix fragments on tiles of 64 pairs for bfloat16 operands whose rows are multiples of 16 bytes.
+// The plan is made for the tile the product kernels will use (`tile_m`).
 #include "common.cuh"
 
 namespace rl {

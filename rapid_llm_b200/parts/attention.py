@@ -20,6 +20,17 @@ head size for keys and values, a multiple of 16: where the two sizes differ, or 
 every head is laid out in the larger one rounded up, with zero weight rows (and zero columns of the
 output projection) for the padding, which changes no score and no output; the q/k norm's mean is
 taken over the true size.  ``names`` maps the tensors' default names to an architecture's own.
+
+A third group of options serves mixers whose q, k and v pass a short causal convolution behind their
+projections (``conv_width`` taps per channel, no activation; the last ``conv_width - 1`` projected rows of
+a request are its state, ``state_need()``): the path from the projection to the cache then runs in float32
+(convolution, rotation from frequencies instead of tables, ``unit_after_rotation``: q and k divided by
+their root mean square after the rotation, without a weight).  ``softcap`` squashes a scaled score ``s``
+to ``softcap * tanh(s / softcap)``; ``sink`` adds one learned term ``exp(sink[head])`` to every row's
+denominator, without a key or a value; ``value_mix`` blends a layer's values with those of the first
+such layer of the model for the same tokens (``"first"`` leaves them in a buffer of the step,
+``"later"`` reads them: ``v <- (1 - m) v + m v_first`` with the learned number ``m``), and the blended
+values are what is cached.
 """
 
 from __future__ import annotations

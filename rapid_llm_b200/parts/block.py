@@ -1,4 +1,4 @@
-"""Arrangement of a layer's parts: the pre-norm residual block.
+"""Arrangements of a layer's parts: the pre-norm residual block, and the block with norms on the outputs.
 
 ``h' = h + Mixer(Norm(h)); h'' = h' + FeedForward(Norm(h'))`` with each add deferred into
 the next norm, so a pair ``(x, residual)`` is threaded through the stack
@@ -9,6 +9,9 @@ Where the parts on both sides of a norm can take it along (``rides_norms``: the 
 it adds to the residual and applies the norm's weight, the product after it applies the row's
 scale), the norm is offered to them and no norm kernel runs; the parts decide step by step
 whether they accept (small steps in bfloat16 do).
+
+``outnorm`` (:class:`OutputNormBlock`): ``h' = h + Norm(Mixer(h)); h'' = h' + Norm(FeedForward(h'))``.  The
+sublayers read the stream itself; the stream is the float32 ``residual`` and ``x`` its rounding.
 """
 
 from __future__ import annotations
